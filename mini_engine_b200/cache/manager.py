@@ -33,6 +33,18 @@ class GroupSpec:
     head_dim: int
     cache_slots: tuple[int, ...]     # the model's cache slots that live in this group
     planes: int = 2                  # 2: keys and values; 1: one row per token and head
+    keep_first: int = 0              # a window group also keeps the pages that hold the sequence's first tokens
+    chunk: Optional[int] = None      # instead of a window: only the chunk that is being filled is kept (chunks from position 0)
+
+    @property
+    def keeps_all(self) -> bool:
+        return self.window is None and self.chunk is None
+
+    def first_needed(self, computed: int) -> int:
+        """The lowest key (beyond the kept first tokens) that a token at position >= ``computed`` can still see."""
+        if self.chunk is not None:
+            return computed // self.chunk * self.chunk
+        return computed - self.window + 1
 
 
 class CacheHolder:
@@ -85,7 +97,7 @@ class CacheManager:
         self.pools = [PagePool(n) for n in num_pages]
         self.state_slots = StateSlotPool(num_state_slots)
         self.prefix_caching = bool(enable_prefix_caching and not has_state and self.groups
-                                   and all(g.window is None for g in self.groups))
+                                   and all(g.keeps_all for g in self.groups))
         self.num_prefix_hit_tokens = 0          # tokens that requests found in the cache instead of computing them
 
     # ---- sizes -----------------------------------------------------------------------
@@ -99,11 +111,17 @@ class CacheManager:
     def fits_at_all(self, num_tokens: int, max_portion: Optional[int] = None) -> bool:
         """Could a request of this many tokens ever be held (with an empty pool)?
 
-        A window group holds at most the window plus the portion being computed."""
+        A window group holds at most the window (and the kept first tokens) plus the portion being computed, a chunk
+        group a chunk plus the portion."""
         need = self.pages_for(num_tokens)
         portion = num_tokens if max_portion is None else min(num_tokens, max_portion)
         for g, pool in zip(self.groups, self.pools):
-            n = need if g.window is None else min(need, self.pages_for(g.window + portion) + 1)
+            if g.keeps_all:
+                n = need
+            elif g.chunk is not None:
+                n = min(need, self.pages_for(g.chunk + portion) + 1)
+            else:
+                n = min(need, self.pages_for(g.window + portion) + 1 + (self.pages_for(g.keep_first) if g.keep_first else 0))
             if n > pool.num_pages:
                 return False
         return True
@@ -194,18 +212,20 @@ class CacheManager:
         holder.num_hashed_blocks = max(holder.num_hashed_blocks, end)
 
     def release_behind_window(self, holder: CacheHolder) -> int:
-        """Give back the pages of window groups that no token still to come can see.
+        """Give back the pages of window and chunk groups that no token still to come can see.
 
         A token at position p >= computed sees keys j > p - window, so a page whose last key
-        lies at or before ``computed - window`` is behind every window to come."""
+        lies at or before ``computed - window`` is behind every window to come; pages that hold any of the
+        ``keep_first`` first tokens stay.  In a chunk group the pages in front of the chunk that position
+        ``computed`` belongs to go."""
         released = 0
         ps = self.page_size
         for g, (spec, pool) in enumerate(zip(self.groups, self.pools)):
-            if spec.window is None or not holder.block_tables:
+            if spec.keeps_all or not holder.block_tables:
                 continue
-            first_needed = holder.num_computed_tokens - spec.window + 1     # lowest key still visible
+            first_needed = spec.first_needed(holder.num_computed_tokens)     # lowest key still visible
             table = holder.block_tables[g]
-            i = holder.num_released[g]
+            i = max(holder.num_released[g], self.pages_for(spec.keep_first) if spec.window is not None else 0)
             while i < len(table) and (i + 1) * ps <= first_needed:
                 if table[i] >= 0:
                     pool.release(table[i])

@@ -380,3 +380,170 @@ class PugadraConfig(ModelConfig):
         if self.side_dim:
             d["token_side"] = {"dim": self.side_dim}
         return d
+
+
+def _positive_ints(raw: dict, keys, where: str) -> dict[str, int]:
+    out = {k: _need(raw, k, int) for k in keys}
+    if any(v < 1 for v in out.values()):
+        raise ConfigError(f"{where}: sizes must be positive: {out}")
+    return out
+
+
+@dataclass
+class GevulornConfig(ModelConfig):
+    """Gevulorn: a decoder whose layers run their mixer and their feed-forward side by side on the same residual stream
+    (x <- x + mixer(norm1(x)) + ff(norm2(x)), layer norms with weight and bias), and of which a range may run several
+    times in a row with the same weights.  config.json keys: ``vocab``, ``width``, ``embedding.scale``, ``norm.eps``,
+    ``logit_softcap`` (absent: none), ``loop`` {start, stop, times} (absent: every layer once) and ``layers``: a list of
+    ``{"type", "mixer", "mlp"}`` with
+
+    * type ``gla``: mixer {heads, dim, vdim, tau} (the rank of the decay's projection is the shape of its tensor's business:
+      ``decay_rank``, absent: read from the weights by whoever has them);
+    * type ``attention``: mixer {heads, kv_heads, dim, vdim, scale, rot {base, dims}, mask {size, keep_first}};
+    * type ``attention_2``: mixer {heads, kv_heads, dim, vdim, scale, softcap, rot {base, dims, scaling {factor, low, high,
+      original}}, mask {size}};
+    * mlp: null, dense {ff} or moe {router {experts, top}, expert {ff}, shared {ff}}.
+
+    ``rot``, ``mask``, ``keep_first``, ``scaling``, ``softcap`` and ``shared`` may be absent.  The design has no limit on
+    positions; ``max_position_embeddings`` is what an int32 position allows the engine."""
+
+    norm_eps: float = 0.0
+    embedding_scale: float = 1.0
+    logit_softcap: float | None = None
+    loop: dict[str, int] | None = None
+    layers: list[dict[str, Any]] = field(default_factory=list)
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "GevulornConfig":
+        layers = _need(raw, "layers", list)
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("config.json key 'layers' must be a list with at least one layer")
+        checked = []
+        for i, layer in enumerate(layers):
+            where = f"layer {i}"
+            kind = layer.get("type") if isinstance(layer, dict) else None
+            if kind not in ("gla", "attention", "attention_2"):
+                raise ConfigError(f"{where}: 'type' must be 'gla', 'attention' or 'attention_2', got {kind!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}: lacks the object 'mixer'")
+            if kind == "gla":
+                m: dict[str, Any] = _positive_ints(mixer, ("heads", "dim", "vdim"), where)
+                m["tau"] = _need(mixer, "tau", float)
+                if not m["tau"] > 0:
+                    raise ConfigError(f"{where}: tau must be positive")
+                if mixer.get("decay_rank") is not None:
+                    m.update(_positive_ints(mixer, ("decay_rank",), where))
+            else:
+                m = _positive_ints(mixer, ("heads", "kv_heads", "dim", "vdim"), where)
+                if m["heads"] % m["kv_heads"]:
+                    raise ConfigError(f"{where}: heads must be a multiple of kv_heads: {m}")
+                m["scale"] = _need(mixer, "scale", float)
+                rot = _opt_object(mixer, "rot", where)
+                if rot is not None:
+                    m["rot"] = {"base": _need(rot, "base", float), "dims": _need(rot, "dims", int)}
+                    if m["rot"]["dims"] % 2 or not 0 <= m["rot"]["dims"] <= m["dim"] or not m["rot"]["base"] > 0:
+                        raise ConfigError(f"{where}: rot.dims must be even and at most dim, rot.base positive: {m['rot']}")
+                    sc = _opt_object(rot, "scaling", where)
+                    if sc is not None:
+                        if kind != "attention_2":
+                            raise ConfigError(f"{where}: only 'attention_2' scales its rotary frequencies")
+                        m["rot"]["scaling"] = {k: _need(sc, k, float) for k in ("factor", "low", "high", "original")}
+                        s = m["rot"]["scaling"]
+                        if not (s["factor"] > 0 and s["original"] > 0 and s["high"] > s["low"] > 0):
+                            raise ConfigError(f"{where}: rot.scaling needs factor > 0, original > 0 and high > low > 0: {s}")
+                mask = _opt_object(mixer, "mask", where)
+                if mask is not None and mask.get("size") is not None:
+                    m["mask"] = {"size": _need(mask, "size", int)}
+                    if m["mask"]["size"] < 1:
+                        raise ConfigError(f"{where}: mask.size must be positive")
+                    if mask.get("keep_first") is not None:
+                        if kind != "attention":
+                            raise ConfigError(f"{where}: only 'attention' keeps first tokens beside its window")
+                        m["mask"]["keep_first"] = _need(mask, "keep_first", int)
+                        if m["mask"]["keep_first"] < 0:
+                            raise ConfigError(f"{where}: mask.keep_first must not be negative")
+                if mixer.get("softcap") is not None:
+                    if kind != "attention_2":
+                        raise ConfigError(f"{where}: only 'attention_2' caps its scores")
+                    m["softcap"] = _need(mixer, "softcap", float)
+                    if not m["softcap"] > 0:
+                        raise ConfigError(f"{where}: softcap must be positive")
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind") not in ("dense", "moe"):
+                    raise ConfigError(f"{where}: 'mlp' must be null or of kind 'dense' or 'moe', got {mlp!r}")
+                if mlp["kind"] == "dense":
+                    mlp = {"kind": "dense", **_positive_ints(mlp, ("ff",), where + " mlp")}
+                else:
+                    router, expert = mlp.get("router"), mlp.get("expert")
+                    if not isinstance(router, dict) or not isinstance(expert, dict):
+                        raise ConfigError(f"{where}: a moe feed-forward needs the objects 'router' and 'expert'")
+                    out = {"kind": "moe", "router": _positive_ints(router, ("experts", "top"), where + " mlp.router"),
+                           "expert": _positive_ints(expert, ("ff",), where + " mlp.expert")}
+                    if out["router"]["top"] > out["router"]["experts"]:
+                        raise ConfigError(f"{where}: router.top must lie between 1 and router.experts")
+                    shared = _opt_object(mlp, "shared", where)
+                    if shared is not None:
+                        out["shared"] = _positive_ints(shared, ("ff",), where + " mlp.shared")
+                    mlp = out
+            checked.append({"type": kind, "mixer": m, "mlp": mlp})
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json lacks the object 'norm'")
+        emb = _opt_object(raw, "embedding", "config.json")
+        loop = _opt_object(raw, "loop", "config.json")
+        if loop is not None:
+            loop = {k: _need(loop, k, int) for k in ("start", "stop", "times")}
+            if not 0 <= loop["start"] <= loop["stop"] <= len(checked) or loop["times"] < 1:
+                raise ConfigError(f"loop must name a range of layers and a positive number of passes: {loop}")
+            if loop["start"] == loop["stop"]:
+                loop = None
+        cap = raw.get("logit_softcap")
+        eos = raw.get("eos_token_id", -1)
+        cfg = cls(architecture=architecture_name(raw), vocab_size=_need(raw, "vocab", int), hidden_size=_need(raw, "width", int),
+                  num_hidden_layers=len(checked), max_position_embeddings=int(raw.get("max_position_embeddings", 1 << 30)),
+                  eos_token_id=-1 if eos is None else int(eos), norm_eps=_need(norm, "eps", float),
+                  embedding_scale=_need(emb, "scale", float) if emb and emb.get("scale") is not None else 1.0,
+                  logit_softcap=_need(raw, "logit_softcap", float) if cap is not None else None, loop=loop, layers=checked)
+        if cfg.vocab_size < 1 or cfg.hidden_size < 1:
+            raise ConfigError("vocab and width must be positive")
+        if not cfg.norm_eps > 0:
+            raise ConfigError("norm.eps must be positive")
+        if cfg.logit_softcap is not None and not cfg.logit_softcap > 0:
+            raise ConfigError("logit_softcap must be positive")
+        return cfg
+
+    def complete_from_tensor_shapes(self, shapes) -> None:
+        """The rank of a gla layer's decay projection, where config.json does not give it, is the row count of the layer's
+        ``mix.a1`` tensor.  ``shapes``: a callable that returns name -> shape (called only when something is missing)."""
+        missing = [i for i, layer in enumerate(self.layers) if layer["type"] == "gla" and "decay_rank" not in layer["mixer"]]
+        if not missing:
+            return
+        found = shapes()
+        for i in missing:
+            shape = found.get(f"l{i}.mix.a1")
+            if shape is None or len(shape) != 2 or shape[0] < 1:
+                raise ConfigError(f"layer {i}: neither config.json (decay_rank) nor the weights (l{i}.mix.a1) give the decay's rank")
+            self.layers[i]["mixer"]["decay_rank"] = int(shape[0])
+
+    def layer_runs(self) -> list[tuple[int, int | None]]:
+        """The order in which layers run as (layer, pass) pairs: ``pass`` is the number of the pass for the first layer of
+        every pass over the looped range (the pass's vector joins the stream there), else None."""
+        n = len(self.layers)
+        if not self.loop:
+            return [(i, None) for i in range(n)]
+        a, b, times = self.loop["start"], self.loop["stop"], self.loop["times"]
+        runs: list[tuple[int, int | None]] = [(i, None) for i in range(a)]
+        for t in range(times):
+            runs += [(i, t if i == a else None) for i in range(a, b)]
+        return runs + [(i, None) for i in range(b, n)]
+
+    def to_json_dict(self) -> dict[str, Any]:
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size, "norm": {"eps": self.norm_eps},
+             "embedding": {"scale": self.embedding_scale}, "layers": self.layers}
+        if self.logit_softcap is not None:
+            d["logit_softcap"] = self.logit_softcap
+        if self.loop:
+            d["loop"] = self.loop
+        return d

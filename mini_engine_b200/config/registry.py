@@ -46,8 +46,27 @@ def registered_architectures() -> list[str]:
 
 
 def load_model_config(folder: str) -> ModelConfig:
+    """The folder's config.json as the architecture's configuration class.  A configuration that leaves a size to the
+    weights (``complete_from_tensor_shapes``) is handed the shapes of the folder's tensors, read from the files' headers."""
     raw = read_config_json(folder)
-    return get_architecture(architecture_name(raw)).config_from_dict(raw)
+    cfg = get_architecture(architecture_name(raw)).config_from_dict(raw)
+    complete = getattr(cfg, "complete_from_tensor_shapes", None)
+    if complete is not None:
+        complete(lambda: tensor_shapes(folder))
+    return cfg
+
+
+def tensor_shapes(folder: str) -> dict[str, tuple[int, ...]]:
+    """Name -> shape of every tensor in the folder's safetensors files (headers only)."""
+    import os
+    from glob import glob
+    from safetensors import safe_open
+    shapes: dict[str, tuple[int, ...]] = {}
+    for path in sorted(glob(os.path.join(os.path.expanduser(folder), "*.safetensors"))):
+        with safe_open(path, "pt", device="cpu") as f:
+            for name in f.keys():
+                shapes[name] = tuple(f.get_slice(name).get_shape())
+    return shapes
 
 
 def _ensure_builtin() -> None:

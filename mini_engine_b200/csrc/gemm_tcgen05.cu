@@ -943,7 +943,7 @@ ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_
 // map_w: W as [E * rows_w, K], boxes bn x 64 (glu: bn / 2 x 64, and rows_w = 2 N: gate rows then up rows); bn: 128 or 256.  C [rows, N]:
 // bfloat16 with ``glu`` (the clamped gated activation), float32 or bfloat16 without.  ``rows`` bounds the grid.
 ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, const int* offsets, int E,
-                                   int rows, int N, int rows_w, int K, int glu, float limit, float alpha, int bn, int* err,
+                                   int rows, int N, int rows_w, int K, int glu, float limit, float alpha, float shift, int bn, int* err,
                                    cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   ME_REQUIRE(map_a && map_w && err && offsets, "me_gemm_tcgen05_grouped: missing operand");
@@ -952,7 +952,7 @@ ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C
   ME_REQUIRE(!glu || c_dtype == ME_BF16, "me_gemm_tcgen05_grouped: the gated activation is written in bfloat16");
   int rc;
   GluParams gp;
-  gp.limit = limit, gp.alpha = alpha, gp.shift = 1.f;
+  gp.limit = limit, gp.alpha = alpha, gp.shift = shift;
   ME_REQUIRE(bn == 128 || bn == 256, "me_gemm_tcgen05_grouped: tile width %d is not 128 or 256", bn);
 #define ME_GROUPED(BN_)                                                                                                          \
   if (glu) rc = launch_grouped<BN_, 1, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);             \

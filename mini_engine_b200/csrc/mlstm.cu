@@ -282,11 +282,12 @@ mlstm_chunk_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int of
   }
 }
 
-// out[t, h*V + v] = o / sqrt(mean_v(o^2) + eps) * w[h*V + v] * sigmoid(g[t, h*V + v]); one warp a head.
+// out[t, h*V + v] = o / sqrt(mean_v(o^2) + eps) * w[h*V + v] * sigmoid(g[t, h*V + v]); one warp a head.  ``w_shared``: the
+// weight has V values that all heads share (w[v]); ``gate_silu``: the gate is g * sigmoid(g) instead of sigmoid(g).
 template <typename TO>
 __global__ void __launch_bounds__(128)
 mlstm_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, int64_t ld, int off_g,
-                 const float* __restrict__ w, float eps, TO* __restrict__ out, int H, int V) {
+                 const float* __restrict__ w, float eps, TO* __restrict__ out, int H, int V, int w_shared, int gate_silu) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -297,7 +298,8 @@ mlstm_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, in
     const float r = 1.0f / sqrtf(warp_sum(ss) / (float)V + eps);
     for (int v = lane; v < V; v += 32) {
       const float g = proj[(int64_t)t * ld + off_g + hd * V + v];
-      out[((int64_t)t * H + hd) * V + v] = from_f<TO>(oo[v] * r * w[hd * V + v] * (1.0f / (1.0f + expf(-g))));
+      const float gate = (gate_silu ? g : 1.0f) / (1.0f + expf(-g));
+      out[((int64_t)t * H + hd) * V + v] = from_f<TO>(oo[v] * r * w[w_shared ? v : hd * V + v] * gate);
     }
   }
 }
@@ -347,11 +349,11 @@ ME_API int me_mlstm_scan(const float* proj, int64_t ld, int off_q, int off_k, in
 }
 
 ME_API int me_mlstm_out(const float* o, const float* proj, int64_t ld, int off_g, const float* w, float eps, void* out,
-                        int out_dtype, int T, int H, int V, cudaStream_t stream) {
+                        int out_dtype, int T, int H, int V, int w_shared, int gate_silu, cudaStream_t stream) {
   if (T == 0) return 0;
   ME_REQUIRE(T > 0 && H > 0 && V > 0, "me_mlstm_out: bad sizes T=%d H=%d V=%d", T, H, V);
   ME_DISPATCH_DTYPE(out_dtype, TO, me_launch(mlstm_out_kernel<TO>, dim3(T), dim3(128), 0, stream, o, proj, ld, off_g, w, eps,
-                                             (TO*)out, H, V));
+                                             (TO*)out, H, V, w_shared, gate_silu));
   ME_LAUNCH_CHECK("me_mlstm_out");
   return 0;
 }

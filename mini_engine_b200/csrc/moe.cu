@@ -154,7 +154,7 @@ template <typename TA, typename TW, typename TO, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ a, int64_t a_stride, const int* __restrict__ sorted, int top,
                 const TW* __restrict__ w, int64_t w_expert_stride, const int* __restrict__ offsets, int E, TO* __restrict__ out,
-                int64_t out_stride, int N, int K, float limit, float alpha) {
+                int64_t out_stride, int N, int K, float limit, float alpha, float shift) {
   __shared__ float As[MG_BM][MG_BK + 1], Ws[MG_BN][MG_BK + 1], Us[GLU ? MG_BN : 1][MG_BK + 1];
   __shared__ int src_row[MG_BM];
   pdl_wait();
@@ -214,7 +214,7 @@ moe_gemm_kernel(const TA* __restrict__ a, int64_t a_stride, const int* __restric
           g = fminf(g, limit);
           u = fminf(fmaxf(u, -limit), limit);
         }
-        v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+        v = g / (1.f + expf(-alpha * g)) * (u + shift);
       }
       out[(int64_t)r * out_stride + n] = from_f<TO>(v);
     }
@@ -297,27 +297,27 @@ ME_API int me_moe_route_sort(const float* z, const float* bias, int T, int E, in
 
 int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top, const void* w, int64_t w_expert_stride,
                     const int* offsets, int E, void* out, int out_dtype, int64_t out_stride, int rows, int N, int K, int glu,
-                    float limit, float alpha, cudaStream_t stream);
+                    float limit, float alpha, float shift, cudaStream_t stream);
 bool me_moe_gemm_mma_takes(int a_dtype, int w_dtype, int64_t a_stride, int N, int K);
 
 // a: [*, K]; sorted: [rows] pair ids (row of a = id / top) or null (a is in expert order); w: [E][glu ? 2N : N][K];
 // offsets: [E + 1]; out: [rows, N] in expert order.  ``rows`` = T * top bounds the grid; the real counts are read on the device.
 ME_API int me_moe_gemm(const void* a, int a_dtype, int64_t a_stride, const int* sorted, int top, const void* w, int w_dtype,
                        int64_t w_expert_stride, const int* offsets, int E, void* out, int out_dtype, int64_t out_stride, int rows,
-                       int N, int K, int glu, float limit, float alpha, int allow_mma, cudaStream_t stream) {
+                       int N, int K, int glu, float limit, float alpha, float shift, int allow_mma, cudaStream_t stream) {
   if (rows == 0) return 0;
   ME_REQUIRE(rows > 0 && N > 0 && K > 0 && E > 0, "me_moe_gemm: bad sizes");
   if (allow_mma && me_moe_gemm_mma_takes(a_dtype, w_dtype, a_stride, N, K))
     return me_moe_gemm_mma(a, a_stride, sorted, top, w, w_expert_stride, offsets, E, out, out_dtype, out_stride, rows, N, K, glu,
-                           limit, alpha, stream);
+                           limit, alpha, shift, stream);
   dim3 grid((rows + MG_BM - 1) / MG_BM + E, (N + MG_BN - 1) / MG_BN);
   ME_DISPATCH_DTYPE(a_dtype, TA, ME_DISPATCH_DTYPE(w_dtype, TW, ME_DISPATCH_DTYPE(out_dtype, TO, {
     if (glu)
       me_launch(moe_gemm_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream, (const TA*)a, a_stride, sorted, top, (const TW*)w,
-                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha);
+                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
     else
       me_launch(moe_gemm_kernel<TA, TW, TO, false>, grid, dim3(256), 0, stream, (const TA*)a, a_stride, sorted, top, (const TW*)w,
-                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha);
+                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
   })));
   ME_LAUNCH_CHECK("me_moe_gemm");
   return 0;

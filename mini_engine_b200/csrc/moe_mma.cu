@@ -21,7 +21,7 @@ template <typename TO, bool GLU>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __restrict__ sorted, int top,
                     const bf16* __restrict__ w, int64_t w_expert_stride, const int* __restrict__ offsets, int E,
-                    TO* __restrict__ out, int64_t out_stride, int N, int K, float limit, float alpha) {
+                    TO* __restrict__ out, int64_t out_stride, int N, int K, float limit, float alpha, float shift) {
   extern __shared__ __align__(16) unsigned char mm_smem[];
   constexpr int HALVES = GLU ? 2 : 1;
   typedef bf16 (*ATile)[MM_BM][MM_LD];
@@ -119,7 +119,7 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __r
           gt = fminf(gt, limit);
           up = fminf(fmaxf(up, -limit), limit);
         }
-        v = gt / (1.f + expf(-alpha * gt)) * (up + 1.f);
+        v = gt / (1.f + expf(-alpha * gt)) * (up + shift);
       }
       out[(int64_t)r * out_stride + n] = from_f<TO>(v);
     }
@@ -134,7 +134,7 @@ bool me_moe_gemm_mma_takes(int a_dtype, int w_dtype, int64_t a_stride, int N, in
 
 int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top, const void* w, int64_t w_expert_stride,
                     const int* offsets, int E, void* out, int out_dtype, int64_t out_stride, int rows, int N, int K, int glu,
-                    float limit, float alpha, cudaStream_t stream) {
+                    float limit, float alpha, float shift, cudaStream_t stream) {
   ME_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && w_expert_stride % 8 == 0,
              "me_moe_gemm: operands of the tensor-core kernel must be 16-byte aligned");
   dim3 grid((rows + MM_BM - 1) / MM_BM + E, (N + MM_BN - 1) / MM_BN);
@@ -149,10 +149,10 @@ int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top,
     }
     if (glu)
       me_launch(moe_gemm_mma_kernel<TO, true>, grid, dim3(MM_THREADS), smem, stream, (const bf16*)a, a_stride, sorted, top,
-                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha);
+                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
     else
       me_launch(moe_gemm_mma_kernel<TO, false>, grid, dim3(MM_THREADS), smem, stream, (const bf16*)a, a_stride, sorted, top,
-                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha);
+                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
   });
   ME_LAUNCH_CHECK("me_moe_gemm (tensor cores)");
   return 0;

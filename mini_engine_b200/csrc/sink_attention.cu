@@ -1,11 +1,16 @@
-// Paged attention with an optional window, an optional sink of score 0 in the softmax's denominator, key and value
-// sizes of their own and an optional sigmoid gate on the output, on the CUDA cores: any sizes up to 256, float32 or
+// Paged attention with an optional mask (a sliding window that may also keep the sequence's first tokens, or chunks), an
+// optional sink in the softmax's denominator (of score 0, or a learned score per head), optionally capped scores, key and
+// value sizes of their own and an optional sigmoid gate on the output, on the CUDA cores: any sizes up to 256, float32 or
 // bfloat16 storage, float32 arithmetic.  It serves portions of prompts (query tiles from the step's tile list) and
 // single tokens (one block per request and head) alike.
 //
 // A request's portion of q_len tokens ends at context length L: local query i sits at position p = L - q_len + i and
 // sees the cached keys j with j <= p and, with a window w, j > p - w.  Weights are exp(s_j) / (sink + sum exp(s_j)),
-// sink = 1 with the sink and 0 without: the running softmax simply starts from maximum 0 and sum 1.  The cache is the
+// sink = 1 with the sink and 0 without: the running softmax simply starts from maximum 0 and sum 1 (from maximum
+// sinks[head] with learned sinks: one more term exp(sinks[head]), neither scaled nor capped).  With ``keep_first`` the
+// window also shows keys j < keep_first; with ``chunk`` (instead of a window) a query sees the keys j <= p of its own
+// chunk, floor(j / chunk) = floor(p / chunk), chunks counted from position 0.  ``softcap`` c > 0: s <- c tanh(s / c)
+// after the scale.  The cache is the
 // engine's usual one, [page][keys | values][kv head][page offset][HD], with HD >= max(D, Dv): a key fills the first D
 // elements of its row, a value the first Dv of its own.  Key tiles start at multiples of SA_BK counted from position 0, so the
 // order of a query's sums does not depend on how the prompt was cut or on what shares the batch.
@@ -22,7 +27,7 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
                  T* __restrict__ out, int64_t out_stride, const T* __restrict__ pool, const int* __restrict__ block_tables,
                  int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                  const int* __restrict__ tiles, int nh, int nkv, int D, int Dv, int HD, int page_size, float scale, int window,
-                 int sink) {
+                 int sink, const float* __restrict__ sinks, float softcap, int keep_first, int chunk) {
   extern __shared__ float smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -49,14 +54,18 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
   const bool row_ok = r < rows;
   const int hi = min(L, start + q0 + rows);  // keys [lo, hi) can be seen by some row of the tile
   int lo = window > 0 ? max(0, start + q0 - window + 1) : 0;
+  if (chunk > 0) lo = (start + q0) / chunk * chunk;
   lo = (lo / SA_BK) * SA_BK;
+  // the tiles that hold kept first tokens come before the window's
+  const int keep_hi = (window > 0 && keep_first > 0) ? min(lo, (min(keep_first, hi) + SA_BK - 1) / SA_BK * SA_BK) : 0;
 
-  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+  float m = sinks ? sinks[head] : (sink ? 0.f : -INFINITY), l = (sinks || sink) ? 1.f : 0.f;
   float acc[SA_MAX / 8];
 #pragma unroll
   for (int k = 0; k < SA_MAX / 8; ++k) acc[k] = 0.f;
 
-  for (int kt = lo; kt < hi; kt += SA_BK) {
+  for (int kt = keep_hi > 0 ? 0 : lo; kt < hi; kt += SA_BK) {
+    if (kt >= keep_hi && kt < lo) kt = lo;
     __syncthreads();                          // previous tile fully consumed (and Q stored)
     for (int idx = tid; idx < SA_BK * row_len; idx += SA_THREADS) {
       const int jj = idx / row_len, d = idx - jj * row_len;
@@ -80,8 +89,11 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
       const int jj = c + 8 * mm, j = kt + jj;
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(Qs[r * ldk + d], Ks[jj * ldk + d], dot);
-      const bool seen = row_ok && j <= p_r && j < L && (window <= 0 || j > p_r - window);
-      s[mm] = seen ? dot * scale : -INFINITY;
+      const bool in_mask = chunk > 0 ? j / chunk == p_r / chunk : (window <= 0 || j > p_r - window || j < keep_first);
+      const bool seen = row_ok && j <= p_r && j < L && in_mask;
+      dot *= scale;
+      if (softcap > 0.f) dot = softcap * tanhf(dot / softcap);
+      s[mm] = seen ? dot : -INFINITY;
       tmax = fmaxf(tmax, s[mm]);
     }
 #pragma unroll
@@ -136,11 +148,12 @@ ME_API int me_sink_attn_tile_q() { return SA_BQ; }
 
 // q: [T, nh*D]; gate: float32 [T, >= nh*Dv] pre-activations or null; out: [T, nh*Dv]; pool: [pages][2][nkv][page_size][HD].
 // tiles: [num_tiles, 2] (request, first local query) for requests that bring several tokens; the first num_decodes
-// requests bring one token each and get one block per head.
+// requests bring one token each and get one block per head.  sinks: [nh] float32 or null; softcap, keep_first, chunk: 0 = none.
 ME_API int me_sink_attn(const void* q, int dtype, int64_t q_stride, const float* gate, int64_t gate_stride, void* out,
                         int64_t out_stride, const void* pool, const int* block_tables, int bt_stride, const int* cu_seqlens,
                         const int* context_lens, const int* tiles, int num_tiles, int num_decodes, int nh, int nkv, int D, int Dv,
-                        int HD, int page_size, float scale, int window, int sink, cudaStream_t stream) {
+                        int HD, int page_size, float scale, int window, int sink, const float* sinks, float softcap,
+                        int keep_first, int chunk, cudaStream_t stream) {
   ME_REQUIRE(D >= 1 && D <= SA_MAX && Dv >= 1 && Dv <= SA_MAX, "me_sink_attn: key size %d / value size %d beyond %d", D, Dv, SA_MAX);
   ME_REQUIRE(HD >= D && HD >= Dv, "me_sink_attn: cache rows of %d elements are too short", HD);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh <= 65535, "me_sink_attn: %d heads, %d kv heads", nh, nkv);
@@ -155,11 +168,11 @@ ME_API int me_sink_attn(const void* q, int dtype, int64_t q_stride, const float*
     if (num_decodes > 0)
       me_launch(sink_attn_kernel<T>, dim3(num_decodes, nh), dim3(SA_THREADS), smem, stream, (const T*)q, q_stride, gate, gate_stride,
                 (T*)out, out_stride, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, (const int*)nullptr, nh, nkv,
-                D, Dv, HD, page_size, scale, window, sink);
+                D, Dv, HD, page_size, scale, window, sink, sinks, softcap, keep_first, chunk);
     if (num_tiles > 0)
       me_launch(sink_attn_kernel<T>, dim3(num_tiles, nh), dim3(SA_THREADS), smem, stream, (const T*)q, q_stride, gate, gate_stride,
                 (T*)out, out_stride, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles, nh, nkv, D, Dv,
-                HD, page_size, scale, window, sink);
+                HD, page_size, scale, window, sink, sinks, softcap, keep_first, chunk);
   });
   ME_LAUNCH_CHECK("me_sink_attn");
   return 0;

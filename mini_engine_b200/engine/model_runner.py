@@ -70,7 +70,7 @@ def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, t
     for slot, needs in enumerate(model.slot_needs):
         for need in needs:
             if isinstance(need, KVCacheNeed):
-                keyed.setdefault((need.window, need.num_kv_heads, need.head_dim, need.planes), []).append(slot)
+                keyed.setdefault((need.window, need.num_kv_heads, need.head_dim, need.planes, need.keep_first, need.chunk), []).append(slot)
             elif isinstance(need, StateNeed):
                 if any(n.name == need.name for n in states.get(slot, [])):
                     raise ValueError(f"cache slot {slot}: two states are named {need.name!r}")
@@ -78,10 +78,10 @@ def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, t
             else:
                 raise TypeError(f"cache slot {slot}: unknown kind of cache need {need!r}")
     groups, location = [], {}
-    for (window, nkv, hd, planes), slots in keyed.items():
+    for (window, nkv, hd, planes, keep_first, chunk), slots in keyed.items():
         for i, s in enumerate(slots):
             location[s] = (len(groups), i)
-        groups.append(GroupSpec(window, nkv, hd, tuple(slots), planes))
+        groups.append(GroupSpec(window, nkv, hd, tuple(slots), planes, keep_first, chunk))
     return groups, location, states
 
 

@@ -8,7 +8,7 @@ GPU) they raise.  The reference builds its kernels with torch's JIT at import
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -27,7 +27,7 @@ _PROTOS = {
     "me_short_conv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_polynorm": [_P, _I, _L, _P, _F, _P, _I, _L, _I, _I, _P],
     "me_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
-    "me_mlstm_out": [_P, _P, _L, _I, _P, _F, _P, _I, _I, _I, _I, _P],
+    "me_mlstm_out": [_P, _P, _L, _I, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P],
     "me_latent_prep": [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "me_latent_attention": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
     "me_heads_to_rows": [_P, _P, _I, _I, _I, _I, _P],
@@ -53,16 +53,23 @@ _PROTOS = {
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
     "me_test_wait_expires": [_P, _I, _P, _P],
     "me_sandwich_norm": [_P, _P, _I, _P, _F, _P, _F, _P, _I, _P, _I, _I, _I, _P],
-    "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _P],
+    "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _F, _P],
     "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "me_rope_table": [_P, _P, _I, _I, _P, _P],
-    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _I, _I, _P],
+    "me_parallel_norm": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
+    "me_attn_prep": [_P, _L, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_gla_decay": [_P, _L, _I, _I, _P, _I, _P, _F, _P, _I, _I, _P],
+    "me_gla_scan": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "me_activation": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _P],
+    "me_soft_cap": [_P, _L, _F, _P],
+    "me_add_row_vector": [_P, _I, _I, _I, _P, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
-    "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _I, _P],
+    "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _F, _I, _P],
     "me_moe_gather": [_P, _I, _L, _P, _I, _P, _I, _I, _P],
-    "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _P, _P],
+    "me_gemm_tcgen05_grouped": [_P, _P, _P, _I, _L, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _I, _P, _P],
     "me_moe_combine": [_P, _L, _P, _P, _I, _P, _I, _L, _P, _I, _L, _I, _I, _P],
     "me_token_side_gate": [_P, _I, _L, _P, _P, _P, _I, _L, _I, _I, _I, _P, _I, _I, _P],
 }
@@ -1104,13 +1111,47 @@ def mlstm_scan(proj: torch.Tensor, offsets: dict, bias_i: torch.Tensor, bias_f: 
 
 
 def mlstm_out(o: torch.Tensor, proj: torch.Tensor, off_g: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
-              num_heads: int, vdim: int) -> None:
-    """Each head's ``o`` divided by its root mean square, times ``weight`` and the sigmoid of the gate columns of ``proj``."""
+              num_heads: int, vdim: int, shared_weight: bool = False, gate: str = "sigmoid") -> None:
+    """Each head's ``o`` divided by its root mean square, times ``weight`` and the sigmoid of the gate columns of ``proj``.
+    ``shared_weight``: the weight has ``vdim`` values that every head uses; ``gate`` "silu": g sigmoid(g) instead of sigmoid(g)."""
     T = o.shape[0]
-    _need(weight.dtype == torch.float32 and weight.numel() == num_heads * vdim, "mlstm_out: weight must be float32 [heads * vdim]")
+    _need(gate in ("sigmoid", "silu"), "mlstm_out: the gate is 'sigmoid' or 'silu'")
+    _need(weight.dtype == torch.float32 and weight.numel() == (vdim if shared_weight else num_heads * vdim),
+          "mlstm_out: weight must be float32 [heads * vdim] ([vdim] when the heads share it)")
     _need(out.is_contiguous() and tuple(out.shape) == (T, num_heads * vdim), "mlstm_out: output shape")
     _call("me_mlstm_out", o.data_ptr(), proj.data_ptr(), proj.stride(0), off_g, weight.data_ptr(), float(eps), out.data_ptr(),
-          _dt(out), T, num_heads, vdim, _stream())
+          _dt(out), T, num_heads, vdim, 1 if shared_weight else 0, 1 if gate == "silu" else 0, _stream())
+
+
+# ---- gated linear attention --------------------------------------------------------------------------
+def gla_decay(proj: torch.Tensor, off_a1: int, rank: int, w2: torch.Tensor, bias: torch.Tensor, tau: float, la: torch.Tensor) -> None:
+    """``la`` [T, C] float32 = logsigmoid(w2 a1 + bias) / tau, with a1 the ``rank`` columns of ``proj`` from ``off_a1`` on: the
+    logarithm of a decay sigmoid(z)^(1/tau) per key channel (see csrc/gla.cu)."""
+    T, C = la.shape
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[0] == T and off_a1 + rank <= proj.shape[1],
+          "gla_decay: projections must be float32 rows that hold the low-rank vector")
+    _need(w2.is_contiguous() and tuple(w2.shape) == (C, rank) and bias.dtype == torch.float32 and bias.numel() == C
+          and la.dtype == torch.float32 and la.is_contiguous(), "gla_decay: w2 [C, rank], float32 bias [C], float32 la [T, C]")
+    _call("me_gla_decay", proj.data_ptr(), proj.stride(0), off_a1, rank, w2.data_ptr(), _dt(w2), bias.data_ptr(), float(tau),
+          la.data_ptr(), T, C, _stream())
+
+
+gla_chunks = True     # portions of prompts run the recurrence a chunk of tokens at a time; a switch for comparisons
+
+
+def gla_scan(proj: torch.Tensor, offsets: dict, la: torch.Tensor, S: torch.Tensor, meta, state_slots: torch.Tensor, o: torch.Tensor,
+             num_heads: int, dim: int, vdim: int, q_scale: float) -> None:
+    """Walks every request's tokens of this step through S_t = diag(exp(la_t)) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t from the
+    state in its slot (see csrc/gla.cu).  ``proj`` [T, N] float32 holds q, k, v at the column ``offsets``; ``la`` [T, heads * dim]
+    and ``o`` [T, heads * vdim] float32."""
+    T = proj.shape[0]
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "gla_scan: projections must be float32 rows")
+    _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (S, la, o)), "gla_scan: float32 state, decays and output")
+    _need(tuple(S.shape[1:]) == (num_heads, dim, vdim) and tuple(la.shape) == (T, num_heads * dim)
+          and tuple(o.shape) == (T, num_heads * vdim), "gla_scan: shapes")
+    _call("me_gla_scan", proj.data_ptr(), proj.stride(0), offsets["q"], offsets["k"], offsets["v"], la.data_ptr(), S.data_ptr(),
+          meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), state_slots.data_ptr(), o.data_ptr(), meta.num_reqs,
+          num_heads, dim, vdim, float(q_scale), 1 if (gla_chunks and T > meta.num_reqs) else 0, _stream())
 
 
 # ---- attention through a latent --------------------------------------------------------------------
@@ -1216,12 +1257,91 @@ def sandwich_norm(residual: torch.Tensor, y: Optional[torch.Tensor], post_weight
           _stream())
 
 
-def clamped_glu(x: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> None:
-    """Rows [gate | up] -> ``g sigmoid(alpha g) (u + 1)`` with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+def parallel_norm(residual: torch.Tensor, adds: Sequence[torch.Tensor], vectors: Sequence[torch.Tensor], eps: float,
+                  norm1: tuple, out1: torch.Tensor, norm2: Optional[tuple] = None, out2: Optional[torch.Tensor] = None,
+                  rows: Optional[torch.Tensor] = None) -> None:
+    """``residual += sum(adds) + sum(vectors)`` (float32, in place; up to two [T, W] tensors of one dtype and two float32 [W]
+    vectors), then one or two layer norms of the new rows: ``out = (x - mean) / sqrt(var + eps) * weight + bias`` with
+    ``norm`` = (weight, bias or None).  With ``rows`` only those rows are computed and ``residual`` is not written."""
+    T, W = residual.shape
+    adds, vectors = [a for a in adds if a is not None], [v for v in vectors if v is not None]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous(), "parallel_norm: the residual must be float32 [T, W]")
+    _need(len(adds) <= 2 and len(vectors) <= 2, "parallel_norm: at most two outputs and two vectors can be added")
+    _need(all(tuple(a.shape) == (T, W) and a.is_contiguous() and a.dtype == adds[0].dtype for a in adds), "parallel_norm: outputs must be [T, W]")
+    _need(all(v.dtype == torch.float32 and v.numel() == W and v.is_contiguous() for v in vectors), "parallel_norm: vectors are float32 [W]")
+    n = T if rows is None else rows.shape[0]
+    for nm, out in ((norm1, out1), (norm2, out2)):
+        if out is None:
+            continue
+        _need(nm is not None and nm[0].dtype == torch.float32 and nm[0].numel() == W and nm[0].is_contiguous()
+              and (nm[1] is None or (nm[1].dtype == torch.float32 and nm[1].numel() == W and nm[1].is_contiguous())),
+              "parallel_norm: weights and biases are float32 [W]")
+        _need(out.is_contiguous() and tuple(out.shape) == (n, W) and out.dtype == out1.dtype, "parallel_norm: output shape")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.is_contiguous()), "parallel_norm: rows must be int32")
+    adds += [None] * (2 - len(adds))
+    vectors += [None] * (2 - len(vectors))
+    _call("me_parallel_norm", residual.data_ptr(), _ptr(adds[0]), _ptr(adds[1]), _dt(adds[0]) if adds[0] is not None else 0,
+          _ptr(vectors[0]), _ptr(vectors[1]), norm1[0].data_ptr(), _ptr(norm1[1]), out1.data_ptr(),
+          _ptr(norm2[0]) if out2 is not None else 0, _ptr(norm2[1]) if out2 is not None else 0, _ptr(out2), _dt(out1), _ptr(rows), n, W,
+          float(eps), _stream())
+
+
+ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """``out = act(x)`` over rows; ``kind`` is a key of ``ACTIVATIONS``."""
+    _need(kind in ACTIVATIONS, f"activation: {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    T, F = x.shape
+    _need(tuple(out.shape) == (T, F) and x.stride(1) == 1 and out.stride(1) == 1, "activation: shapes")
+    _call("me_activation", x.data_ptr(), _dt(x), x.stride(0), out.data_ptr(), _dt(out), out.stride(0), T, F, ACTIVATIONS[kind], _stream())
+
+
+def soft_cap(x: torch.Tensor, cap: float) -> None:
+    """``x <- cap * tanh(x / cap)`` in place (float32)."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and cap > 0, "soft_cap: float32 values and a positive cap")
+    _call("me_soft_cap", x.data_ptr(), x.numel(), float(cap), _stream())
+
+
+def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> None:
+    """``x[t] += v`` for every row (in place)."""
+    _need(x.dim() == 2 and x.is_contiguous() and v.dtype == torch.float32 and v.is_contiguous() and v.numel() == x.shape[1],
+          "add_row_vector: x [T, W] and a float32 vector [W]")
+    _call("me_add_row_vector", x.data_ptr(), _dt(x), x.shape[0], x.shape[1], v.data_ptr(), _stream())
+
+
+def attn_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
+              norm: Optional[str], eps: float, freq: Optional[torch.Tensor], positions: torch.Tensor,
+              slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor, pool: Optional[torch.Tensor], page_size: int,
+              num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> None:
+    """From the packed float32 projections q|k|v (the leading columns of ``proj``): bias, a weighted RMS norm of every q and k
+    head in front of the rotation (``norm`` "before") or a plain one behind it ("after"), the rotation of element i with
+    element i + len(freq) by position x ``freq`` (float64 frequencies), queries to ``q_out`` and keys and values into the
+    cache rows that ``slot_mapping`` names (see csrc/attn_prep.cu)."""
+    T = proj.shape[0]
+    C = num_heads * dim + num_kv_heads * (dim + vdim)
+    _need(norm in (None, "before", "after"), "attn_prep: norm is None, 'before' or 'after'")
+    _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= C, "attn_prep: projections must be float32 rows")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == C), "attn_prep: bias must be float32 [channels]")
+    _need(norm != "before" or all(w is not None and w.dtype == torch.float32 and w.numel() == dim for w in (q_norm, k_norm)),
+          "attn_prep: the norm in front of the rotation needs float32 weights [dim]")
+    _need(freq is None or (freq.dtype == torch.float64 and freq.is_contiguous() and 2 * freq.numel() <= dim), "attn_prep: freq must be float64 [<= dim / 2]")
+    _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, num_heads * dim), "attn_prep: query output shape")
+    _need(slot_mapping is None or (pool is not None and pool.is_contiguous() and pool.dim() == 5 and pool.shape[1] == 2
+                                   and pool.shape[-1] >= max(dim, vdim) and pool.dtype == q_out.dtype),
+          "attn_prep: the cache must be [pages, 2, kv heads, page, >= max(dim, vdim)] of the activations' dtype")
+    rot = 2 * freq.numel() if freq is not None else 0
+    _call("me_attn_prep", proj.data_ptr(), proj.stride(0), _ptr(bias), _ptr(q_norm), _ptr(k_norm), {None: 0, "before": 1, "after": 2}[norm],
+          float(eps), _ptr(freq) if rot else 0, rot, positions.data_ptr(), _ptr(slot_mapping), q_out.data_ptr(), _ptr(pool), _dt(q_out),
+          pool.shape[-1] if pool is not None else 0, page_size, num_heads, num_kv_heads, dim, vdim, T, _stream())
+
+
+def clamped_glu(x: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float = 1.0) -> None:
+    """Rows [gate | up] -> ``g sigmoid(alpha g) (u + shift)`` with g = min(gate, limit), u = clamp(up, -limit, limit)."""
     T, F2 = x.shape
     _need(F2 % 2 == 0 and tuple(out.shape) == (T, F2 // 2) and x.stride(1) == 1 and out.stride(1) == 1, "clamped_glu: shapes")
     _call("me_clamped_glu", x.data_ptr(), _dt(x), x.stride(0), out.data_ptr(), _dt(out), out.stride(0), T, F2 // 2, float(limit),
-          float(alpha), _stream())
+          float(alpha), float(shift), _stream())
 
 
 def conv_rope_kv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_weight: Optional[torch.Tensor],
@@ -1272,10 +1392,14 @@ use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor
 
 def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, pool: torch.Tensor, page_size: int,
                    block_tables: torch.Tensor, meta, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
-                   window: Optional[int], sink: bool) -> None:
+                   window: Optional[int], sink: bool, sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
+                   keep_first: int = 0, chunk: Optional[int] = None) -> None:
     """Attention over the paged cache with keys of ``dim`` and values of ``vdim`` elements: ``q`` [T, heads * dim] -> ``out``
     [T, heads * vdim]; a query at position p sees keys p - window < j <= p; with ``sink`` the softmax's denominator has one
     more term, exp(0); ``gate`` (float32 rows of pre-activations, heads * vdim wide) multiplies the output by its sigmoid.
+    ``sinks`` (float32 [heads]): the term is exp(sinks[head]) instead; ``softcap`` c: scores become c tanh(s / c) after the
+    scale; ``keep_first``: the window also shows keys j < keep_first; ``chunk`` (instead of a window): a query sees the keys
+    j <= p with floor(j / chunk) = floor(p / chunk).
 
     bfloat16 with keys and values of 64 or 128 elements (the cache row's size) runs the engine's tensor-core kernels, the
     tcgen05 one for portions of prompts and the split-K one for single tokens; everything else the CUDA-core kernel of
@@ -1289,8 +1413,12 @@ def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
     _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[1] == num_heads * vdim),
           "sink_attention: the gate must be float32 rows")
     _need(block_tables.dtype == torch.int32 and block_tables.stride(1) == 1, "sink_attention: block tables")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads and sinks.is_contiguous()),
+          "sink_attention: learned sinks are float32 [heads]")
+    _need(not (chunk and window), "sink_attention: a window or chunks, not both")
+    plain = sinks is None and not softcap and not keep_first and not chunk      # what the tensor-core kernels know
     decodes, tiles_left = meta.num_decodes, True
-    fast = (use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
+    fast = (plain and use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
             and meta.error_flag is not None and q.is_contiguous() and q.data_ptr() % 16 == 0)
     if fast and decodes:
         attention_decode(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window, sink=sink, gate=gate)
@@ -1306,7 +1434,8 @@ def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
         _call("me_sink_attn", q.data_ptr(), _dt(q), q.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0, out.data_ptr(),
               out.stride(0), pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
               meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles, decodes, num_heads, num_kv_heads, dim, vdim, HD, page_size,
-              float(scale), int(window or 0), 1 if sink else 0, _stream())
+              float(scale), int(window or 0), 1 if sink else 0, _ptr(sinks), float(softcap or 0.0), int(keep_first or 0),
+              int(chunk or 0), _stream())
 
 
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, weights: torch.Tensor) -> None:
@@ -1351,10 +1480,11 @@ MOE_TCGEN05_MIN_ROWS = 512   # (token, choice) pairs from which the experts' pro
 
 
 def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, offsets: torch.Tensor,
-             out: torch.Tensor, glu: Optional[tuple[float, float]] = None, workspace=None, err: Optional[torch.Tensor] = None) -> None:
+             out: torch.Tensor, glu: Optional[tuple] = None, workspace=None, err: Optional[torch.Tensor] = None) -> None:
     """One product per expert: ``weight`` [E, N or 2N, K]; the rows of ``a`` are gathered through ``order`` (pair id // top) or,
-    without it, lie in expert order already; ``out`` [pairs, N] in expert order.  ``glu`` = (limit, alpha): the weight holds gate
-    rows then up rows and the result is the clamped gated activation.
+    without it, lie in expert order already; ``out`` [pairs, N] in expert order.  ``glu`` = (limit, alpha[, shift]): the weight holds gate
+    rows then up rows and the result is the gated activation g sigmoid(alpha g) (u + shift), clamped by a positive limit (shift 1
+    when it is not given).
 
     bfloat16 operands with K a multiple of 8 run on the tensor cores: from ``MOE_TCGEN05_MIN_ROWS`` pairs on (and with
     ``workspace`` and ``err`` given) the tcgen05 kernel of csrc/gemm_tcgen05.cu over rows brought into expert order first,
@@ -1364,7 +1494,7 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
     rows = out.shape[0]
     _need(weight.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and out.stride(1) == 1 and out.shape[1] == N, "moe_gemm: shapes")
     _need(order is not None or a.shape[0] == rows, "moe_gemm: rows in expert order")
-    limit, alpha = glu if glu else (0.0, 0.0)
+    limit, alpha, shift = (tuple(glu) + (1.0,))[:3] if glu else (0.0, 0.0, 0.0)
     if (use_moe_mma and use_tcgen05_gemm and workspace is not None and err is not None and rows >= MOE_TCGEN05_MIN_ROWS
             and a.dtype == weight.dtype == torch.bfloat16 and K % 8 == 0 and weight.data_ptr() % 16 == 0
             and (out.dtype == torch.bfloat16 or (not glu and out.dtype == torch.float32))):
@@ -1376,12 +1506,12 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
             bn = moe_tcgen05_tile_n if moe_tcgen05_tile_n else (256 if N >= 256 else 128)
             _call("me_gemm_tcgen05_grouped", matrix_tensor_map(a, 128).ptr, matrix_tensor_map(weight.view(E * NN, K), bn // 2 if glu else bn).ptr,
                   out.data_ptr(), _dt(out), out.stride(0), offsets.data_ptr(), E, rows, N, NN, K, 1 if glu else 0, float(limit),
-                  float(alpha), bn, err.data_ptr(), _stream())
+                  float(alpha), float(shift), bn, err.data_ptr(), _stream())
             return
         order = None
     _call("me_moe_gemm", a.data_ptr(), _dt(a), a.stride(0), _ptr(order), top, weight.data_ptr(), _dt(weight), weight.stride(0),
           offsets.data_ptr(), E, out.data_ptr(), _dt(out), out.stride(0), rows, N, K, 1 if glu else 0, float(limit), float(alpha),
-          1 if use_moe_mma else 0, _stream())
+          float(shift), 1 if use_moe_mma else 0, _stream())
 
 
 def moe_combine(rows: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor) -> None:

@@ -45,11 +45,15 @@ class ParamDecl:
 @dataclass(frozen=True)
 class KVCacheNeed:
     """Paged keys and values: ``window=None`` keeps every key, else the last ``window``.  ``planes``: 2 for keys and
-    values, 1 for a cache with one row per token and head (a latent that serves as both)."""
+    values, 1 for a cache with one row per token and head (a latent that serves as both).  ``keep_first``: a window that
+    also keeps the sequence's first tokens for good.  ``chunk`` (instead of a window): only the keys of the chunk that is
+    being filled are kept, chunks of this many tokens counted from position 0."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
+    keep_first: int = 0
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -80,6 +84,15 @@ class NormedUpdate:
     weight: "torch.Tensor"
     eps: float
     mult: float
+
+
+@dataclass
+class PendingSum:
+    """What a block whose sub-layers run side by side returns instead of a plain output: the ``outputs`` ([T, width] each, at
+    most two) and ``vectors`` (float32 [width] each, e.g. a projection's bias left to be added) have not joined the residual
+    stream yet; the next kernel that reads the stream (the next norm, or the model's last) adds them all first."""
+    outputs: list
+    vectors: list = field(default_factory=list)
 
 
 @dataclass

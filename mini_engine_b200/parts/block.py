@@ -10,7 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
-from .base import NormedUpdate, ParamDecl, Part, StreamUpdate, Upcoming
+from .base import NormedUpdate, ParamDecl, Part, PendingSum, StreamUpdate, Upcoming
 from .registry import PartSpec, build_part, register_block
 
 
@@ -233,6 +233,42 @@ class SandwichNormBlock(Block):
         return update
 
 
+class ParallelBlock(Block):
+    """A block whose mixer and feed-forward read the same residual stream, each through a norm of its own:
+    x <- x + (mixer(norm1(x)) + feed_forward(norm2(x))); the feed-forward may be absent.  Both outputs are left pending
+    (``PendingSum``) and join the stream in the kernel that reads it next, which also computes both norms of the new rows in
+    one pass; a mixer's output bias (``output_bias()``) is deferred the same way.  A ``LayerCall`` may name a pass vector
+    (``add_row``) that joins the stream right before the block's norms.  The norms must be of a kind that takes a
+    ``PendingSum`` (a layer norm with a bias)."""
+    capturable = True
+    feed_forward_optional = True
+    takes_pass_vector = True
+
+    def __init__(self, spec: BlockSpec, shared: Optional[dict] = None):
+        super().__init__(spec, shared)
+        self.pass_vectors = (shared or {}).get("pass_vectors")
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "_sum_and_norm"):
+                raise ValueError("a 'parallel' block needs norms that can add a pending sum (kind 'layernorm')")
+        if hasattr(self.mixer, "defer_output_bias"):
+            self.mixer.defer_output_bias = True
+
+    def forward(self, residual, delta, ctx, call, upcoming=None):
+        vectors = []
+        if call.add_row is not None:
+            vectors.append(self.pass_vectors.row(call.add_row))
+        also = (self.feed_forward_norm, "norm_out2") if self.feed_forward is not None else None
+        h = self.mixer_norm._sum_and_norm(residual, delta, ctx, None, "norm_out", None, vectors=vectors, also=also)
+        h1, h2 = h if also is not None else (h, None)
+        pending = PendingSum([self.mixer.forward(h1, ctx, call)])
+        bias = self.mixer.output_bias() if hasattr(self.mixer, "output_bias") else None
+        if bias is not None:
+            pending.vectors.append(bias)
+        if self.feed_forward is not None:
+            pending.outputs.append(self.feed_forward.forward(h2, ctx))
+        return pending
+
+
 @dataclass(frozen=True)
 class SharedRef:
     """Stands in a PartSpec's args for an object that the model builds once and shares."""
@@ -242,3 +278,4 @@ class SharedRef:
 register_block("pre_norm", PreNormBlock)
 register_block("hyper_connection", HyperConnectionBlock)
 register_block("sandwich_norm", SandwichNormBlock)
+register_block("parallel", ParallelBlock)

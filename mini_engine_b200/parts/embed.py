@@ -37,12 +37,13 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     capturable = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None, param: str = "weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None, param: str = "weight", softcap: float | None = None):
         super().__init__()
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
         self.param = param
+        self.softcap = float(softcap) if softcap else None     # logits <- cap * tanh(logits / cap)
 
     def param_decls(self):
         return [ParamDecl(self.param, (self.vocab_size, self.hidden_size), tied_to=self.tied_to)]
@@ -51,4 +52,6 @@ class LMHead(Part):
         out = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
         ops.tag = "logits"
         ops.linear(x, self.p(self.param), out, workspace=ctx.buffer, err=ctx.error_flag)
+        if self.softcap:
+            ops.soft_cap(out, self.softcap)
         return out

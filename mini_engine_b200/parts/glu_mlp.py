@@ -1,7 +1,8 @@
 """Gated feed-forwards whose two halves are clamped, dense or as a mixture of routed experts.
 
 One expert (and the dense form): g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit),
-y = g * sigmoid(alpha * g) * (u + 1), output W_down y; ``limit`` None: nothing is clamped.
+y = g * sigmoid(alpha * g) * (u + shift), output W_down y; ``limit`` None: nothing is clamped.  ``alpha`` 1 and ``shift`` 0
+is the plain SiLU-gated form silu(g) * u.
 
 ``RoutedExperts``: router logits z = W_router h + b in float32; the ``top`` experts with the largest logits are chosen
 and weighted by the softmax over the chosen logits only; the output is the weighted sum of their outputs, plus a
@@ -24,11 +25,12 @@ class ClampedGLU(FeedForward):
     capturable = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, limit: Optional[float] = None, alpha: float = 1.702,
-                 gate: str = "gate", up: str = "up", down: str = "down"):
+                 shift: float = 1.0, gate: str = "gate", up: str = "up", down: str = "down"):
         super().__init__()
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.limit = float(limit) if limit is not None else 0.0
         self.alpha = float(alpha)
+        self.shift = float(shift)
         self.gate_up = Linear(hidden_size, [(gate, intermediate_size), (up, intermediate_size)], name="gate_up")
         self.down = Linear(intermediate_size, [(down, hidden_size)], name=down)
 
@@ -45,16 +47,16 @@ class ClampedGLU(FeedForward):
                 and ops.tcgen05_takes(x, w)):
             # a long step: the activation is the epilogue of the tcgen05 product, as SiLU is in a SwiGLU
             ops.tag = out_name + "_act"
-            ops.linear_tcgen05(x, w, act, "silu_mul", ctx.error_flag, glu=(self.limit, self.alpha, 1.0))
+            ops.linear_tcgen05(x, w, act, "silu_mul", ctx.error_flag, glu=(self.limit, self.alpha, self.shift))
         elif (ctx.act_dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
               and ops.decode_linear_takes(x.shape[0], self.hidden_size, w, False)):
             # a step of up to 16 tokens: the same in the epilogue of the decode products
             ops.tag = out_name + "_act"
             ops.decode_linear(w, x, out=act, epilogue="silu_mul", fetch_ahead=self.down.weight, err=ctx.error_flag,
-                              glu=(self.limit, self.alpha, 1.0))
+                              glu=(self.limit, self.alpha, self.shift))
         else:
             z = self.gate_up.forward(x, ctx, out_name + "_gate_up")
-            ops.clamped_glu(z, act, self.limit, self.alpha)
+            ops.clamped_glu(z, act, self.limit, self.alpha, self.shift)
         return self.down.forward(act, ctx, out_name, out_dtype=out_dtype)
 
 
@@ -62,13 +64,14 @@ class RoutedExperts(FeedForward):
     capturable = True
 
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, limit: Optional[float] = None,
-                 alpha: float = 1.702, router_bias: bool = True, shared: Optional[dict] = None):
+                 alpha: float = 1.702, shift: float = 1.0, router_bias: bool = True, shared: Optional[dict] = None):
         super().__init__()
         if not 1 <= top <= num_experts:
             raise ValueError(f"{top} of {num_experts} experts cannot be chosen")
         self.hidden_size, self.num_experts, self.top, self.expert_size = hidden_size, num_experts, top, expert_size
         self.limit = float(limit) if limit is not None else 0.0
         self.alpha = float(alpha)
+        self.shift = float(shift)
         self.has_router_bias = router_bias
         self.router = Linear(hidden_size, [("router", num_experts)], name="router")
         self.shared = ClampedGLU(hidden_size, **shared) if shared else None
@@ -108,7 +111,7 @@ class RoutedExperts(FeedForward):
         place = ctx.buffer("moe_place", (T * top,), torch.int32)
         ops.moe_route_sort(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt, counts, offsets, order, place)
         act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)
-        ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha), workspace=ctx.buffer, err=ctx.error_flag)
+        ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha, self.shift), workspace=ctx.buffer, err=ctx.error_flag)
         rows = ctx.buffer("moe_rows", (T * top, W), torch.float32)
         ops.moe_gemm(act, None, top, self._down, offsets, rows, workspace=ctx.buffer, err=ctx.error_flag)
         shared = self.shared.forward(x, ctx, out_name="moe_shared") if self.shared is not None else None

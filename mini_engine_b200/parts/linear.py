@@ -38,6 +38,10 @@ class Linear(Part):
     def first_weight(self):
         return self.weight
 
+    def fuses(self, x, ctx, activation: str) -> bool:
+        """Whether this product's kernel for a step of this shape applies ``activation`` to its results itself."""
+        return False
+
     def forward(self, x, ctx, out_name: str, *, out_dtype: Optional[torch.dtype] = None,
                 epilogue: str = "none", may_split: bool = False, residual: Optional[torch.Tensor] = None,
                 next_norm=None, fetch_ahead: Optional[torch.Tensor] = None):

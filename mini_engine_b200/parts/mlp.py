@@ -41,4 +41,34 @@ class SwiGLU(FeedForward):
                                       fetch_ahead=upcoming.weight if upcoming else None)
 
 
+class ActivationMLP(FeedForward):
+    """``down(act(up(x)))`` with an element-wise activation (a key of ``ops.ACTIVATIONS``; "relu_squared" is max(z, 0)^2)."""
+    capturable = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu_squared", up: str = "up", down: str = "down"):
+        super().__init__()
+        from .. import ops
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.up = Linear(hidden_size, [(up, intermediate_size)], name=up)
+        self.down = Linear(intermediate_size, [(down, hidden_size)], name=down)
+
+    def sub_parts(self):
+        return [("", self.up), ("", self.down)]
+
+    def first_weight(self):
+        return self.up.weight
+
+    def forward(self, x, ctx, out_name: str = "ffn_out"):
+        from .. import ops
+        z = self.up.forward(x, ctx, out_name + "_up", epilogue=self.activation if self.up.fuses(x, ctx, self.activation) else "none")
+        if not self.up.fuses(x, ctx, self.activation):
+            act = ctx.buffer(out_name + "_act", tuple(z.shape), ctx.act_dtype)
+            ops.activation(z, act, self.activation)
+            z = act
+        return self.down.forward(z, ctx, out_name)
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("activation_mlp", ActivationMLP)

@@ -27,6 +27,7 @@ class LayerCall:
     cache_slot: int
     writes_cache: bool = True
     kv_slot: "Optional[int]" = None    # a mixer that reads ANOTHER call's keys and values: the cache slot that holds them
+    add_row: "Optional[int]" = None    # the row of the model's pass vectors that joins the stream right before this call
 
 
 @dataclass
@@ -49,6 +50,25 @@ class ModelPlan:
     tables: dict[str, tuple[str, int, int]] = field(default_factory=dict)   # key -> (tensor name, rows, columns): tables
                                        # indexed by token that blocks share (``SharedRef(key)`` in a ``BlockSpec``'s args)
     streams: int = 1                   # residual streams; > 1: the residual is [streams, T, hidden], all equal at the start
+    logit_softcap: "Optional[float]" = None   # logits <- cap * tanh(logits / cap)
+    pass_vectors: "Optional[tuple[str, int]]" = None   # (tensor name, rows): vectors of ``hidden_size`` values of which a
+                                       # ``LayerCall.add_row`` names one (what each pass over looped layers adds to the stream)
+
+
+class PassVectors(Part):
+    """Vectors [rows, width] that the model owns; a ``LayerCall`` with ``add_row`` has one of them added to the residual
+    stream right before its block runs (by the block's first kernel: the block kind must set ``takes_pass_vector``)."""
+    capturable = True
+
+    def __init__(self, name: str, rows: int, width: int):
+        super().__init__()
+        self.name, self.rows, self.width = name, rows, width
+
+    def param_decls(self):
+        return [ParamDecl(self.name, (self.rows, self.width), role="vector")]
+
+    def row(self, i: int) -> torch.Tensor:
+        return self.p(self.name)[i]
 
 
 class DecoderModel(Part):
@@ -62,10 +82,13 @@ class DecoderModel(Part):
                                     param=plan.embed_param)
         self.tables = {k: TokenEmbedding(rows, cols, param=name) for k, (name, rows, cols) in plan.tables.items()}
         self.shared.update(self.tables)
+        self.pass_vectors = None
+        if plan.pass_vectors is not None:
+            self.pass_vectors = self.shared["pass_vectors"] = PassVectors(plan.pass_vectors[0], plan.pass_vectors[1], plan.hidden_size)
         self.blocks = [build_block(s, self.shared) for s in plan.blocks]
         self.final_norm = build_part("norm", plan.final_norm)
         tied = plan.embed_prefix + plan.embed_param if plan.tie_word_embeddings else None
-        self.head = LMHead(plan.vocab_size, plan.hidden_size, tied, param=plan.head_param)
+        self.head = LMHead(plan.vocab_size, plan.hidden_size, tied, param=plan.head_param, softcap=plan.logit_softcap)
         self.schedule = list(plan.schedule)
         n_slots = 1 + max((c.cache_slot for c in self.schedule), default=-1)
         # What each cache slot must hold, taken from the first call that uses it.
@@ -74,6 +97,12 @@ class DecoderModel(Part):
         for c in self.schedule:
             if not 0 <= c.block < len(self.blocks):
                 raise ValueError(f"schedule names block {c.block}, the model has {len(self.blocks)}")
+            if c.add_row is not None:
+                if not getattr(self.blocks[c.block], "takes_pass_vector", False):
+                    raise ValueError(f"block {c.block} ({plan.blocks[c.block].kind!r}) cannot add a pass vector in front of itself")
+                if self.pass_vectors is None or not 0 <= c.add_row < self.pass_vectors.rows:
+                    raise ValueError(f"the schedule names pass vector {c.add_row}, the model has "
+                                     f"{self.pass_vectors.rows if self.pass_vectors else 0}")
             needs = self.blocks[c.block].cache_needs()
             if not self.slot_needs[c.cache_slot]:
                 self.slot_needs[c.cache_slot] = needs
@@ -90,6 +119,8 @@ class DecoderModel(Part):
     def sub_parts(self):
         parts = [(self.plan.embed_prefix, self.embed)]
         parts += [("", t) for t in self.tables.values()]
+        if self.pass_vectors is not None:
+            parts.append(("", self.pass_vectors))
         parts += [(self.plan.block_prefix.format(i=i), b) for i, b in enumerate(self.blocks)]
         parts += [(self.plan.final_norm_prefix, self.final_norm), (self.plan.head_prefix, self.head)]
         return parts

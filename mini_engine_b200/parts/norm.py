@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import AddedToResidual, Norm, NormedUpdate, ParamDecl, PendingNorm, StreamUpdate
+from .base import AddedToResidual, Norm, NormedUpdate, ParamDecl, PendingNorm, PendingSum, StreamUpdate
 from .registry import register_norm
 
 
@@ -68,25 +68,56 @@ class LayerNorm(Norm):
     residual stream or several: with ``streams`` > 1 the residual is [streams, T, size] and the norm reads
     u = sum_s mix_in[s] x_s (every stream once when no ``mix_in`` is given: the sum of the streams).  A pending
     ``StreamUpdate`` (or, with one stream, a plain output still to be added) goes into the streams in the same pass.
-    ``param``: the weight's name on disk, for models that do not call it ``weight``."""
+    ``param``: the weight's name on disk, for models that do not call it ``weight``.  ``bias``: the name of a bias that is
+    added behind the weight (one stream only); such a norm also takes a pending ``PendingSum`` (several outputs and vectors
+    still to be added) and may be computed together with a second norm of the same rows (``also=(norm, out_name)``: a
+    block whose sub-layers both read the stream)."""
     capturable = True
 
-    def __init__(self, size: int, eps: float, streams: int = 1, param: str = "weight"):
+    def __init__(self, size: int, eps: float, streams: int = 1, param: str = "weight", bias: Optional[str] = None):
         super().__init__()
+        if bias is not None and streams != 1:
+            raise ValueError("LayerNorm: a bias is supported over one residual stream only")
         self.size = size
         self.eps = float(eps)
         self.streams = streams
         self.param = param
+        self.bias = bias
         self._ones = None
 
     def param_decls(self):
-        return [ParamDecl(self.param, (self.size,), init="norm", role="vector")]
+        decls = [ParamDecl(self.param, (self.size,), init="norm", role="vector")]
+        if self.bias is not None:
+            decls.append(ParamDecl(self.bias, (self.size,), role="vector"))
+        return decls
+
+    def weight_and_bias(self):
+        return self.p(self.param), (self.p(self.bias) if self.bias is not None else None)
+
+    def _sum_and_norm(self, residual, delta, ctx, rows, out_name, out_dtype, vectors=(), also=None):
+        """One pass of ``parallel_norm``: everything pending joins the stream, then this norm (and ``also``'s)."""
+        outputs, vectors = [], list(vectors)
+        if isinstance(delta, PendingSum):
+            outputs, vectors = list(delta.outputs), list(delta.vectors) + vectors
+        elif isinstance(delta, torch.Tensor):
+            outputs = [delta]
+        elif delta is not None and not isinstance(delta, AddedToResidual):
+            raise TypeError(f"LayerNorm with a bias cannot add a pending {type(delta).__name__}")
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        dtype = out_dtype or ctx.act_dtype
+        out = ctx.buffer(out_name, (n, self.size), dtype)
+        out2 = ctx.buffer(also[1], (n, self.size), dtype) if also is not None else None
+        ops.parallel_norm(residual, outputs, vectors, self.eps, self.weight_and_bias(), out,
+                          also[0].weight_and_bias() if also is not None else None, out2, rows=rows)
+        return out if also is None else (out, out2)
 
     def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False, *,
                 mix_in: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, out_name: str = "norm_out",
                 conv=None):
         """``conv`` = (weight, state or None): in a step where every request brings one token, the short convolution that
         follows the norm (h + conv(h), its state moved on) runs in the norm's kernel; the result is then that sum."""
+        if residual.dim() == 2 and mix_in is None and conv is None and (self.bias is not None or isinstance(delta, PendingSum)):
+            return self._sum_and_norm(residual, delta, ctx, rows, out_name, out_dtype)
         streams = residual if residual.dim() == 3 else residual.unsqueeze(0)
         update = None
         if isinstance(delta, StreamUpdate):

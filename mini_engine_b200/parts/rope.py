@@ -60,5 +60,51 @@ class InterleavedRotary(PositionEncoding):
         self.inv_freq = (self.theta ** (-i / d) if d else i).contiguous().to(device)
 
 
+class FrequencyRotary(PositionEncoding):
+    """Rotary positions in the half-split layout (element i with element i + rotary_dim / 2) on the first ``rotary_dim``
+    elements, from a table of frequencies instead of a table over positions: f_i = theta^(-2i / rotary_dim), optionally
+    rescaled by wavelength (``scaling`` = {factor, low, high, original}, the rule Llama 3.1 uses for long contexts: with
+    l = 2 pi / f, a frequency with l < original / high stays, one with l > original / low is divided by factor, and between
+    the two (1 - s) f / factor + s f with s = (original / l - low) / (high - low)).  The kernels form each angle from the
+    position and ``freq`` (float64, so that the angle is rounded once), which leaves the longest position open."""
+    capturable = True
+
+    layout = "half_split"
+
+    def __init__(self, rotary_dim: int, theta: float, scaling: "dict | None" = None):
+        super().__init__()
+        if rotary_dim % 2 or rotary_dim < 0:
+            raise ValueError(f"rotary_dim {rotary_dim} must be even")
+        self.rotary_dim = rotary_dim
+        self.theta = float(theta)
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling:
+            s = self.scaling
+            if not (s["factor"] > 0 and s["original"] > 0 and s["high"] > s["low"] > 0):
+                raise ValueError(f"rotary scaling needs factor > 0, original > 0 and high > low > 0, got {s}")
+        self.freq: torch.Tensor | None = None
+
+    def frequencies(self) -> list[float]:
+        import math
+        d = self.rotary_dim
+        out = []
+        for i in range(d // 2):
+            f = self.theta ** (-2.0 * i / d)
+            if self.scaling:
+                s = self.scaling
+                wavelength = 2.0 * math.pi / f
+                if wavelength > s["original"] / s["low"]:
+                    f = f / s["factor"]
+                elif not wavelength < s["original"] / s["high"]:
+                    t = (s["original"] / wavelength - s["low"]) / (s["high"] - s["low"])
+                    f = (1.0 - t) * f / s["factor"] + t * f
+            out.append(f)
+        return out
+
+    def finalize(self, dtype, device):
+        self.freq = torch.tensor(self.frequencies(), dtype=torch.float64).contiguous().to(device)
+
+
 register_position_encoding("rope", RotaryEmbedding)
+register_position_encoding("rope_frequencies", FrequencyRotary)
 register_position_encoding("rope_interleaved", InterleavedRotary)
