@@ -446,8 +446,6 @@ class GevulornConfig(ModelConfig):
                         raise ConfigError(f"{where}: rot.dims must be even and at most dim, rot.base positive: {m['rot']}")
                     sc = _opt_object(rot, "scaling", where)
                     if sc is not None:
-                        if kind != "attention_2":
-                            raise ConfigError(f"{where}: only 'attention_2' scales its rotary frequencies")
                         m["rot"]["scaling"] = {k: _need(sc, k, float) for k in ("factor", "low", "high", "original")}
                         s = m["rot"]["scaling"]
                         if not (s["factor"] > 0 and s["original"] > 0 and s["high"] > s["low"] > 0):
@@ -464,8 +462,6 @@ class GevulornConfig(ModelConfig):
                         if m["mask"]["keep_first"] < 0:
                             raise ConfigError(f"{where}: mask.keep_first must not be negative")
                 if mixer.get("softcap") is not None:
-                    if kind != "attention_2":
-                        raise ConfigError(f"{where}: only 'attention_2' caps its scores")
                     m["softcap"] = _need(mixer, "softcap", float)
                     if not m["softcap"] > 0:
                         raise ConfigError(f"{where}: softcap must be positive")

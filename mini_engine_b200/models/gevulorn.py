@@ -42,7 +42,8 @@ def gevulorn_plan(cfg: GevulornConfig) -> ModelPlan:
             args = {"hidden_size": W, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"],
                     "scale": m["scale"], "norm_eps": eps, "position_encoding": _rotation(m, shared), "sink": True}
             if kind == "attention":
-                args.update(qk_norm="after", bias=False, mask=("window", mask["size"], mask.get("keep_first", 0)) if mask else None)
+                args.update(qk_norm="after", bias=False, softcap=m.get("softcap"),
+                            mask=("window", mask["size"], mask.get("keep_first", 0)) if mask else None)
             else:
                 args.update(qk_norm="before", bias=True, softcap=m.get("softcap"), mask=("chunk", mask["size"]) if mask else None)
             mixer = PartSpec("masked_sink_attention", args)

@@ -40,6 +40,8 @@ class ParamDecl:
     sources: list[DiskSource] = field(default_factory=list)   # empty: one tensor, same name
     role: str = "matrix"                   # "matrix" | "vector" (vectors are held in float32)
     tied_to: Optional[str] = None          # full name of the parameter whose storage is shared
+    optional: bool = False                 # a tensor that a file may hold although this model has no use for it: loaded if
+                                           # it is there (so that it is not reported as unexpected), never missed
 
 
 @dataclass(frozen=True)

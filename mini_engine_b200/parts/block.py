@@ -253,6 +253,16 @@ class ParallelBlock(Block):
         if hasattr(self.mixer, "defer_output_bias"):
             self.mixer.defer_output_bias = True
 
+    def param_decls(self):
+        """A layer without a feed-forward has no use for the second norm; files that hold one all the same are accepted."""
+        if self.feed_forward is not None:
+            return []
+        spec = self.spec.feed_forward_norm or self.spec.norm
+        if spec is None or "size" not in spec.args:
+            return []
+        names = [spec.args.get("param", "weight")] + ([spec.args["bias"]] if spec.args.get("bias") else [])
+        return [ParamDecl(self.spec.feed_forward_norm_prefix + n, (spec.args["size"],), role="vector", optional=True) for n in names]
+
     def forward(self, residual, delta, ctx, call, upcoming=None):
         vectors = []
         if call.add_row is not None:

@@ -53,6 +53,7 @@ class _Expected:
     param: str            # full parameter name
     row_start: int
     shape: tuple[int, ...]
+    optional: bool = False
 
 
 def iter_param_decls(model: Part) -> Iterator[tuple[str, Part, ParamDecl]]:
@@ -70,9 +71,9 @@ def expected_disk_tensors(model: Part) -> dict[str, _Expected]:
         full = prefix + decl.name
         if decl.sources:
             for src in decl.sources:
-                exp[prefix + src.disk_name] = _Expected(full, src.row_start, (src.rows, *decl.shape[1:]))
+                exp[prefix + src.disk_name] = _Expected(full, src.row_start, (src.rows, *decl.shape[1:]), decl.optional)
         else:
-            exp[full] = _Expected(full, 0, tuple(decl.shape))
+            exp[full] = _Expected(full, 0, tuple(decl.shape), decl.optional)
     return exp
 
 
@@ -92,7 +93,8 @@ def load_weights(model: Part, folder: str, dtype: torch.dtype, device) -> dict[s
                 sl = f.get_slice(name)
                 found[name] = (path, tuple(sl.get_shape()), _ST_DTYPES.get(sl.get_dtype(), torch.float32))
 
-    missing = [n for n in expected if n not in found]
+    missing = [n for n, e in expected.items() if n not in found and not e.optional]
+    absent = {e.param for n, e in expected.items() if n not in found and e.optional}      # optional and not in the files
     # A tied head's own tensor may be present on disk; it is skipped (utils/loader.py:23-24).
     unexpected = [n for n in found if n not in expected and n not in tied_names]
     wrong = [(n, found[n][1], e.shape) for n, e in expected.items() if n in found and found[n][1] != e.shape]
@@ -104,11 +106,12 @@ def load_weights(model: Part, folder: str, dtype: torch.dtype, device) -> dict[s
     decl_of: dict[str, tuple[Part, ParamDecl]] = {}
     stored: dict[str, list[torch.dtype]] = {}
     for name, e in expected.items():
-        stored.setdefault(e.param, []).append(found[name][2])
+        if name in found:
+            stored.setdefault(e.param, []).append(found[name][2])
     for prefix, part, decl in iter_param_decls(model):
         full = prefix + decl.name
         decl_of[full] = (part, decl)
-        if decl.tied_to is not None:
+        if decl.tied_to is not None or full in absent:
             continue
         kinds = stored[full]
         if all(k in _INTS for k in kinds):
@@ -121,7 +124,8 @@ def load_weights(model: Part, folder: str, dtype: torch.dtype, device) -> dict[s
 
     by_file: dict[str, list[str]] = {}
     for name in expected:
-        by_file.setdefault(found[name][0], []).append(name)
+        if name in found:
+            by_file.setdefault(found[name][0], []).append(name)
     for path, names in by_file.items():
         with safe_open(path, "pt", device="cpu") as f:
             for name in names:
@@ -135,5 +139,6 @@ def load_weights(model: Part, folder: str, dtype: torch.dtype, device) -> dict[s
             if decl.tied_to not in params:
                 raise WeightsError(folder, [f"{full} is tied to {decl.tied_to}, which the model lacks"], [], [])
             params[full] = params[decl.tied_to]
-        part.params[decl.name] = params[full]
+        if full in params:
+            part.params[decl.name] = params[full]
     return params

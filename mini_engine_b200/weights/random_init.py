@@ -34,7 +34,7 @@ def random_state_dict(model: DecoderModel, seed: int, dtype: torch.dtype = torch
     gen.manual_seed(int(seed))
     init_of = {}
     for prefix, _, decl in iter_param_decls(model):
-        if decl.tied_to is not None:
+        if decl.tied_to is not None or decl.optional:
             continue
         names = [prefix + s.disk_name for s in decl.sources] or [prefix + decl.name]
         for n in names:
@@ -82,6 +82,8 @@ def init_random_on_device(model: DecoderModel, seed: int, dtype: torch.dtype, de
         full = prefix + decl.name
         if decl.tied_to is not None:
             tied.append((full, part, decl))
+            continue
+        if decl.optional:
             continue
         if decl.role == "vector":
             t = torch.empty(decl.shape, dtype=torch.float32, device=device).normal_(0.0, 1.0, generator=gen)
