@@ -28,8 +28,9 @@ GPU: for ``--gpus N`` with N > 1 one line says so and the exit code is 2.
 Modes: ``step`` (the line above), ``offline`` (the reference's own bench.py:38-66 with its options ``--num-seqs
 --budget --chunked --threshold --out --label --expect-gpu``; a JSON row like the reference's is appended to
 ``--out``), ``mixed`` (the 8B workload above, at any shape), ``decode`` (decode at batches ``--batches`` after
-``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen`` and ``pugadra``
-(prefill and decode of that design at the layer sizes ``--sizes``, beside the Qwen3 of equal size, with the time of every kernel).
+``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen``, ``pugadra`` and ``gevulorn``
+(prefill and decode of that design at the layer sizes ``--sizes``, beside the Qwen3 of equal size (Gevulorn: the Pugadra of equal
+size), with the time of every kernel).
 """
 from __future__ import annotations
 
@@ -100,7 +101,7 @@ def _pugadra(width, layers, ff, heads, kv_heads, dim, window, experts, top, expe
     moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff, "limit": 7.0},
            "shared": {"ff": shared_ff, "limit": 7.0}}
     cfg = {"architecture": "Pugadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.3,
-           "token_side": {"dim": side},
+           **({"token_side": {"dim": side}} if side else {}),
            "layers": [{"type": "attention", "mixer": mixer(i), "mlp": moe if i % 2 else {"kind": "dense", "ff": ff, "limit": 7.0}}
                       for i in range(layers)]}
     twin = _qwen3(layers, width, heads, kv_heads, ff, True, head_dim=dim, vocab_size=vocab, use_sliding_window=True,
@@ -113,7 +114,37 @@ PUGADRA_SIZES = {   # width, layers, ff, heads / kv heads / head size, window, e
     "m": _pugadra(2048, 8, 8192, 16, 4, 128, 1024, 32, 2, 2048, 2048, 128),
     "l": _pugadra(4096, 6, 12288, 32, 8, 128, 1024, 32, 4, 2048, 4096, 256),
 }
-DESIGN_SIZES = {"logozen": LOGOZEN_SIZES, "pugadra": PUGADRA_SIZES}
+def _gevulorn(width, layers, ff, heads, kv_heads, dim, window, experts, top, expert_ff, shared_ff, g_heads, g_dim, g_vdim, vocab=32768):
+    """A Gevulorn of ``layers`` layers: gated linear attention on the even layers (the first with a dense feed-forward), on the
+    odd ones attention by turns with a window that keeps four first tokens and with chunks, capped scores and rescaled
+    frequencies; routed experts beside a shared one everywhere but in the first layer; capped logits.  And the Pugadra of the
+    same width, depth, heads, head size, window, feed-forward and expert sizes and vocabulary to set beside it."""
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": expert_ff}, "shared": {"ff": shared_ff}}
+
+    def layer(i):
+        if i % 2 == 0:
+            return {"type": "gla", "mixer": {"heads": g_heads, "dim": g_dim, "vdim": g_vdim, "tau": 16.0, "decay_rank": 16},
+                    "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe}
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5}
+        if i % 4 == 1:
+            m.update(rot={"base": 10000.0, "dims": dim}, mask={"size": window, "keep_first": 4})
+            return {"type": "attention", "mixer": m, "mlp": moe}
+        m.update(rot={"base": 1000000.0, "dims": dim, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}},
+                 mask={"size": window}, softcap=30.0)
+        return {"type": "attention_2", "mixer": m, "mlp": moe}
+    cfg = {"architecture": "Gevulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": width ** 0.5},
+           "logit_softcap": 30.0, "layers": [layer(i) for i in range(layers)]}
+    twin, _ = _pugadra(width, layers, ff, heads, kv_heads, dim, window, experts, top, expert_ff, shared_ff, 0, vocab=vocab)
+    return cfg, twin
+
+
+GEVULORN_SIZES = {   # as PUGADRA_SIZES, then the recurrence's heads / key size / value size
+    "s": _gevulorn(1024, 8, 3072, 16, 4, 64, 512, 16, 2, 768, 768, 8, 64, 128),
+    "m": _gevulorn(2048, 8, 8192, 16, 4, 128, 1024, 32, 2, 2048, 2048, 8, 128, 256),
+    "l": _gevulorn(4096, 6, 12288, 32, 8, 128, 1024, 32, 4, 2048, 4096, 16, 128, 256),
+}
+DESIGN_SIZES = {"logozen": LOGOZEN_SIZES, "pugadra": PUGADRA_SIZES, "gevulorn": GEVULORN_SIZES}
+DESIGN_TWINS = {"logozen": "qwen3", "pugadra": "qwen3", "gevulorn": "pugadra"}      # the model set beside each design
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
@@ -123,8 +154,8 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen", "pugadra"], default="step")
-    p.add_argument("--sizes", default="s,m", help="logozen and pugadra modes: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
+    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen", "pugadra", "gevulorn"], default="step")
+    p.add_argument("--sizes", default="s,m", help="logozen, pugadra and gevulorn modes: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
     p.add_argument("--shape", choices=sorted(SHAPES), default="0.6b", help="layer sizes, when no --model is given")
     p.add_argument("--extras", type=int, default=1,
                    help="step mode: also run the offline workload, the 8B mixed workload and the 32B decode points")
@@ -754,6 +785,53 @@ def _pugadra_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> di
     return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_moe_gemm", "me_gemm_tcgen05_grouped"), times, pk)
 
 
+def _seen_pairs(T: int, mask) -> float:
+    """(query, key) pairs of a prompt of T tokens under a Gevulorn mask: a window with kept first tokens, or chunks."""
+    if not mask:
+        return T * (T + 1) / 2
+    size, keep = mask["size"], mask.get("keep_first")
+    if keep is None and "keep_first" not in mask and mask.get("chunked"):
+        full, rest = divmod(T, size)
+        return full * size * (size + 1) / 2 + rest * (rest + 1) / 2
+    pairs = _window_pairs(T, size)
+    if keep:
+        pairs += sum(min(keep, max(0, p - size + 1)) for p in range(T))
+    return pairs
+
+
+def _gevulorn_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
+    """What Gevulorn's own kernels have to move or do in a prefill step of T tokens and the fraction of the measured peak that
+    their summed time makes: bytes for the element-wise kernels, multiply-adds for attention, recurrence and experts."""
+    W = cfg["width"]
+    need = {k: 0.0 for k in ("me_parallel_norm", "me_attn_prep", "me_sink_attn", "me_attn_prefill_tcgen05", "me_gla_decay", "me_gla_scan",
+                             "me_mlstm_out", "me_activation", "me_clamped_glu", "me_moe_gemm", "me_gemm_tcgen05_grouped", "me_moe_combine")}
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        H, D, V = m["heads"], m["dim"], m["vdim"]
+        need["me_parallel_norm"] += T * W * (8 + 2 * item + (2 * item if mlp is not None else item))   # stream in and out, two y in, h out
+        if layer["type"] == "gla":
+            need["me_gla_decay"] += T * H * D * 4 + T * m.get("decay_rank", 16) * 4
+            # the recurrence itself: k v^T into the state and the state times q, for every token
+            need["me_gla_scan"] += 4.0 * H * D * V * T
+            need["me_mlstm_out"] += T * H * V * (8 + item)
+        else:
+            G = m["kv_heads"]
+            need["me_attn_prep"] += T * (H + 2 * G) * D * (4 + item)
+            mask = dict(m["mask"], chunked=layer["type"] == "attention_2") if m.get("mask") else None
+            att = 2.0 * H * (D + V) * _seen_pairs(T, mask)
+            need["me_sink_attn"] += att
+            need["me_attn_prefill_tcgen05"] += att
+        if mlp is not None and mlp["kind"] == "dense":
+            need["me_activation"] += T * mlp["ff"] * 2 * item
+        elif mlp is not None:
+            need["me_moe_gemm"] += 6.0 * T * mlp["router"]["top"] * mlp["expert"]["ff"] * W
+            need["me_gemm_tcgen05_grouped"] += 6.0 * T * mlp["router"]["top"] * mlp["expert"]["ff"] * W
+            need["me_moe_combine"] += T * W * (4 * mlp["router"]["top"] + 2 * item)
+            if mlp.get("shared"):
+                need["me_clamped_glu"] += T * mlp["shared"]["ff"] * 3 * item
+    return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_gla_scan", "me_moe_gemm", "me_gemm_tcgen05_grouped"), times, pk)
+
+
 def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
     """The like kernels of the Qwen3 beside a design: its norm, its q/k preparation and its prompt attention."""
     W, L = cfg["hidden_size"], cfg["num_hidden_layers"]
@@ -773,11 +851,12 @@ def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict
 
 
 def run_design_mode(args, design: str) -> int:
-    """Prefill and decode throughput of a design at layer sizes that resemble real models', beside the Qwen3 of the same
-    width, depth, heads, feed-forward width and vocabulary; random weights drawn on the device."""
+    """Prefill and decode throughput of a design at layer sizes that resemble real models', beside the Qwen3 (for Gevulorn the
+    Pugadra) of the same width, depth, heads, feed-forward width and vocabulary; random weights drawn on the device."""
     import torch
     sizes_of = DESIGN_SIZES[design]
-    roofline = {"logozen": _logozen_roofline, "pugadra": _pugadra_roofline}[design]
+    rooflines = {"logozen": _logozen_roofline, "pugadra": _pugadra_roofline, "gevulorn": _gevulorn_roofline, "qwen3": _qwen3_roofline}
+    twin_label = DESIGN_TWINS[design]
     pk = peaks()
     item = 2 if args.dtype in ("bfloat16", "bf16") else 4
     T = args.prompt_len or 2048
@@ -785,7 +864,7 @@ def run_design_mode(args, design: str) -> int:
     rows = {}
     for size in [x for x in args.sizes.split(",") if x]:
         cfg, twin = sizes_of[size]
-        for label, c in ((design, cfg), ("qwen3", twin)):
+        for label, c in ((design, cfg), (twin_label, twin)):
             model = Model.of_config(c, f"{label} {size}", args.seed)
             top = max(batches)
             llm = make_engine(model, args, max_seqs=top + 2, budget=max(T, top), context=T + 256,   # (a state slot each, and the prompt's)
@@ -801,12 +880,12 @@ def run_design_mode(args, design: str) -> int:
             times = _kernel_times(runner, cache, prompt, prompts[:min(8, top)])
             row["kernels_prefill_us"] = times["prefill"]
             row["kernels_decode_b8_us"] = times["decode"]
-            row["roofline_prefill"] = (roofline if label == design else _qwen3_roofline)(c, T, item, pk, times["prefill"])
+            row["roofline_prefill"] = rooflines[label](c, T, item, pk, times["prefill"])
             rows[f"{label}_{size}"] = row
             del llm, runner, cache
             release_memory()
     print(json.dumps({"mode": design, "dtype": args.dtype, "peaks": pk["source"], "prompt_tokens": T,
-                      "decode_context": T // 2, "sizes": {k: {design: v[0], "qwen3": v[1]} for k, v in sizes_of.items()
+                      "decode_context": T // 2, "sizes": {k: {design: v[0], twin_label: v[1]} for k, v in sizes_of.items()
                                                           if k in args.sizes.split(",")}, "results": rows}))
     return 0
 

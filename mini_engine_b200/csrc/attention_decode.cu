@@ -448,6 +448,10 @@ struct DecodePrep {
   const float* cos_sin;       // rotary table [positions][HD] (cos | sin) or null; the token's position is context - 1
   const int* slot_mapping;    // [tokens] cache slot of the token's key and value; null: another layer wrote them
   bf16* pool;                 // the cache slot, [page][k|v][kv_head][offset][HD]
+  // the mask and the scores of the tensor-map kernel (all 0: a plain window)
+  int keep_first;             // a window also shows the keys j < keep_first
+  int chunk;                  // instead of a window: the keys of the query's own chunk, from floor(p / chunk) * chunk on
+  float softcap;              // c > 0: scores become c tanh(score * scale / c)
 };
 
 // The two products are mma.sync m16n8k16 with ldmatrix.
@@ -491,10 +495,12 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   };
   int page_ahead = -1;
   if (warp == 0 && lane < n_pages) page_ahead = page_of(z * part_keys);
-  const int lo_w = window > 0 ? max(0, L - window) : 0;
+  const int keep = prep.keep_first;
+  const int w_eff = prep.chunk > 0 ? (L - 1) % prep.chunk + 1 : window;       // the query sits at L - 1
+  const int lo_w = w_eff > 0 ? max(0, L - w_eff) : 0;
   const int part_lo = z * part_keys, part_hi = min(L, part_lo + part_keys);
   const int64_t slot0 = ((int64_t)b * nh + kvh * G + g0) * max_parts + z;
-  if (part_hi <= part_lo || part_hi <= lo_w) {
+  if (part_hi <= part_lo || (part_hi <= lo_w && part_lo >= keep)) {
     pdl_wait();
     pdl_launch_dependents();
     if (part_lo < L || z == 0)
@@ -529,7 +535,8 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   const bool makes_new = FUSED && has_new && prep.slot_mapping != nullptr;
   const bool wait_first = has_new && !makes_new;
   // the tiles of the partition that hold keys the request sees: [t_first, n_tiles)
-  const int t_first = (TILED && lo_w > part_lo) ? (lo_w - part_lo) / DEC_PART : 0;
+  // (a partition that holds kept first keys walks all its tiles: those between them and the window are masked whole)
+  const int t_first = (TILED && lo_w > part_lo && part_lo >= keep) ? (lo_w - part_lo) / DEC_PART : 0;
   const int n_tiles = TILED ? (part_hi - part_lo + DEC_PART - 1) / DEC_PART : 1;
   int tile_lo = part_lo + t_first * DEC_PART, tile_hi = min(part_hi, tile_lo + DEC_PART);
   if (t_first > 0 && warp == 0 && lane < n_pages) page_ahead = page_of(tile_lo);
@@ -552,7 +559,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     first_row = -1;
     if (warp == 0 && lane < n_pages) {
       const int j0 = tile_lo + lane * page_size;
-      const int page = (j0 < tile_hi && j0 + page_size > lo_w) ? page_ahead : -1;
+      const int page = (j0 < tile_hi && (j0 + page_size > lo_w || j0 < keep)) ? page_ahead : -1;
       if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size;
     }
   };
@@ -676,7 +683,10 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
       }
     }
   };
-  const float sl2 = scale * 1.4426950408889634f;
+  const float cap = prep.softcap;
+  const float sl2 = cap > 0.f ? 1.4426950408889634f : scale * 1.4426950408889634f;
+  const float cap_in = cap > 0.f ? scale * 1.4426950408889634f * (2.0f / cap) : 0.f;
+  const float scale_m = cap > 0.f ? 1.0f : scale;         // what brings a maximum to natural-log units
   const int mi = lane >> 3;
   // Each warp keeps the running maximum, sum and output of its 32 keys of every tile (rows g and g + 8 of the strip);
   // the sums stay per thread until the end (the factor a new maximum brings is the same for the four threads of a row).
@@ -733,7 +743,11 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = tile_lo + warp * 32 + i * 8 + 2 * t4 + e;
-        if (j >= tile_hi || j < lo_w) s[i][e] = s[i][e + 2] = -INFINITY;
+        if (cap > 0.f) {                               // c tanh(x) = c (1 - 2 / (1 + 2^(2 log2(e) x)))
+          s[i][e] = cap - 2.0f * cap * __frcp_rn(1.0f + exp2f(s[i][e] * cap_in));
+          s[i][e + 2] = cap - 2.0f * cap * __frcp_rn(1.0f + exp2f(s[i][e + 2] * cap_in));
+        }
+        if (j >= tile_hi || (j < lo_w && j >= keep)) s[i][e] = s[i][e + 2] = -INFINITY;
       }
       tm0 = fmaxf(tm0, fmaxf(s[i][0], s[i][1]));
       tm1 = fmaxf(tm1, fmaxf(s[i][2], s[i][3]));
@@ -773,7 +787,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
     if (newest_here && warp == 1) put_new(vs, 1);
     {                                                // rows of V that are no keys of this request: zero
       const int j = tile_lo + tid;                   // 128 threads, 128 rows
-      if (j >= tile_hi || j < lo_w)
+      if (j >= tile_hi || (j < lo_w && j >= keep))
         for (int p = 0; p < PIECES; ++p) *reinterpret_cast<uint4*>(v_at(tid, p)) = make_uint4(0, 0, 0, 0);
     }
     __syncthreads();                                 // V complete and cleaned; every warp is done reading K
@@ -801,7 +815,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
   if (VBUF < 2) __syncthreads();                     // every warp is done reading V: K's tile now takes the warps' results
   if (!landed && tid == 0) atomicOr(err + 1, 1);     // a load did not land in time: the result is reported as invalid
-  merge_warps_of_partition<HD>(reinterpret_cast<float*>(ks), w_m, w_l, w_f, w_fl, o, mx0, l0, mx1, l1, n_g, sl2, scale, tmp_out,
+  merge_warps_of_partition<HD>(reinterpret_cast<float*>(ks), w_m, w_l, w_f, w_fl, o, mx0, l0, mx1, l1, n_g, sl2, scale_m, tmp_out,
                                tmp_m, tmp_l, slot0, max_parts);
 }
 
@@ -834,10 +848,13 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const int* __restrict__ context_lens,
                                     const float* __restrict__ tmp_out, const float* __restrict__ tmp_m,
                                     const float* __restrict__ tmp_l, int nh, int hd, int max_parts, int part_keys,
-                                    int sink, const float* __restrict__ gate, int64_t gate_stride) {
+                                    int sink, const float* __restrict__ gate, int64_t gate_stride,
+                                    const float* __restrict__ sinks) {
   constexpr int CHUNK = 128;                         // partitions whose factors are held in shared memory at a time
   __shared__ float f_s[CHUNK], red[32];
   const int b = blockIdx.x, h = blockIdx.y;
+  const float sink_score = sinks ? sinks[h] : 0.f;   // a learned score instead of 0 (a parameter, not made by this step)
+  sink = sink || sinks != nullptr;
   const int L = context_lens[b];                     // written by the host, not by a kernel of this step
   const int64_t tok = cu_seqlens[b];
   pdl_wait();
@@ -855,10 +872,10 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
       lv[p] = p < P ? tmp_l[row0 + p] : 0.f;
       ov[p] = (p < P && tid < hd) ? tmp_out[(row0 + p) * hd + tid] : 0.f;     // (never written where mv is -inf: not used then)
     }
-    float M = sink ? 0.f : -INFINITY;                // the sink: a key of score 0 that has no value
+    float M = sink ? sink_score : -INFINITY;         // the sink: a key of score 0 (or a learned one) that has no value
 #pragma unroll
     for (int p = 0; p < 16; ++p) M = fmaxf(M, mv[p]);
-    float lt = sink ? expf(-M) : 0.f, acc = 0.f;
+    float lt = sink ? expf(sink_score - M) : 0.f, acc = 0.f;
 #pragma unroll
     for (int p = 0; p < 16; ++p) {                   // partitions in index order
       if (mv[p] == -INFINITY) continue;
@@ -879,9 +896,9 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
   mx = warp_max(mx);
   if (lane == 0) red[warp] = mx;
   __syncthreads();
-  float M = sink ? 0.f : -INFINITY;
+  float M = sink ? sink_score : -INFINITY;
   for (int w = 0; w < nwarps; ++w) M = fmaxf(M, red[w]);
-  float lt = sink ? expf(-M) : 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};      // thread t owns columns t, t + blockDim, ... (hd <= 4 blockDim)
+  float lt = sink ? expf(sink_score - M) : 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};      // thread t owns columns t, t + blockDim, ... (hd <= 4 blockDim)
   for (int p0 = 0; p0 < P && M > -INFINITY; p0 += CHUNK) {
     const int n = min(CHUNK, P - p0);
     __syncthreads();
@@ -967,7 +984,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
                           int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                           int window, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts,
                           int* err, int kind, const void* kv_map, int sink, const float* gate, int64_t gate_stride,
-                          cudaStream_t stream) {
+                          int keep_first, int chunk, float softcap, const float* sinks, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 256, "me_attn_decode: head_dim %d is not a multiple of 8 up to 256", hd);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode: %d heads, %d kv heads", nh, nkv);
@@ -991,8 +1008,17 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
              "me_attn_decode: kernel kind %d does not take this shape", kind);
   const bool tma_mma = kind == 4 || (kind == 0 && tma_mma_ok);
   const bool mma = !tma_mma && (kind == 3 || (kind == 0 && mma_ok));
+  // keep_first (with a window), chunk (instead of one) and softcap are the tensor-map kernel's alone; sinks: float32 [nh],
+  // the extra term of the softmax is exp(sinks[head]) (added once, in the merge).
+  ME_REQUIRE(keep_first >= 0 && chunk >= 0 && softcap >= 0.f && !(chunk > 0 && window > 0) && (keep_first == 0 || window > 0),
+             "me_attn_decode: a window (with kept first keys) or chunks, not both");
+  ME_REQUIRE(tma_mma || (keep_first == 0 && chunk == 0 && softcap == 0.f),
+             "me_attn_decode: kept first keys, chunks and capped scores need the kernel fed by tensor-map loads");
   if (tma_mma) {
-    const DecodePrep none = {};
+    DecodePrep none = {};
+    none.keep_first = keep_first;
+    none.chunk = chunk;
+    none.softcap = softcap;
     int rc = hd == 64 ? launch_partition_tma_mma<64, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none)
                       : launch_partition_tma_mma<128, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
@@ -1023,7 +1049,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const int mthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(decode_merge_kernel<T>, mgrid, dim3(mthreads), 0, stream,
       (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART, sink, gate,
-      gate_stride)));
+      gate_stride, sinks)));
   ME_LAUNCH_CHECK("me_attn_decode (merge)");
   return 0;
 }
@@ -1092,7 +1118,8 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   ME_LAUNCH_CHECK("me_attn_decode_fused (partitions)");
   dim3 mgrid(num_reqs, nh);
   me_launch(decode_merge_kernel<bf16>, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream, (bf16*)out, out_row_stride, cu_seqlens,
-            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART * tiles, 0, (const float*)nullptr, (int64_t)0);
+            context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART * tiles, 0, (const float*)nullptr, (int64_t)0,
+            (const float*)nullptr);
   ME_LAUNCH_CHECK("me_attn_decode_fused (merge)");
   return 0;
 }

@@ -371,14 +371,19 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap q_map, const __g
 // are brought to the final reference and added at the end.
 // Parities: a wait names a phase of its barrier by parity, which is only right while the phase before it is
 // over.  Every wait below stands where that is known (the comment beside it says why).
-template <int HD>
+// EXTRA: kept first keys, chunks, capped scores and learned sinks are compiled in (the plain kernel keeps its registers).
+template <int HD, bool EXTRA>
 __global__ void __launch_bounds__(TA_THREADS)
 attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                                        bf16* __restrict__ out, int64_t out_row_stride, const int* __restrict__ block_tables,
                                        int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                                        const int* __restrict__ tiles, int nh, int nkv, int gp, int page_size, float scale_log2,
                                        int window, int sink, const float* __restrict__ gate, int64_t gate_stride,
-                                       int* __restrict__ err) {
+                                       int* __restrict__ err, int keep_first_arg, int chunk_arg, float softcap_arg,
+                                       const float* __restrict__ sinks_arg) {
+  const int keep_first = EXTRA ? keep_first_arg : 0, chunk = EXTRA ? chunk_arg : 0;
+  const float softcap = EXTRA ? softcap_arg : 0.f;
+  const float* __restrict__ sinks = EXTRA ? sinks_arg : nullptr;
   constexpr int KEYS = 128, HALVES = HD / 64;
   constexpr int Q_BYTES = TA_ROWS * HD * 2, KV_BYTES = KEYS * HD * 2, RING = 3;
   constexpr int HALF_BYTES = 128 * 128, KB_BYTES = KEYS * 128;
@@ -402,10 +407,18 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
   const int L = context_lens[b], start = L - q_len;
   const int n_tok = min(tq, q_len - q0);
   const int p_lo = start + q0, p_hi = p_lo + n_tok - 1, hi = p_hi + 1;
-  int lo = window > 0 ? max(0, p_lo - window + 1) : 0;
+  // The keys some row of the tile sees: [lo_seen, hi) under a window or in chunks (a row then sees its own chunk, from
+  // floor(p / chunk) * chunk on), and with ``keep_first`` also [0, keep_first).  Tiles of keys: first the ones that hold kept
+  // keys in front of the window's first tile, then from that tile on.
+  int lo = window > 0 ? max(0, p_lo - window + 1) : (chunk > 0 ? (p_lo / chunk) * chunk : 0);
   const int lo_seen = lo;
   lo = (lo / KEYS) * KEYS;
-  const int n_tiles = (hi - lo + KEYS - 1) / KEYS;
+  const int n_first = keep_first > 0 ? min((keep_first + KEYS - 1) / KEYS, lo / KEYS) : 0;
+  const int n_tiles = n_first + (hi - lo + KEYS - 1) / KEYS;
+  auto tile_start = [&](int it) { return (EXTRA && it < n_first) ? it * KEYS : lo + (it - n_first) * KEYS; };
+  // With a cap c the scores become c tanh(s * scale / c) before anything else; exponents then take log2(e) alone.
+  const float sl2 = softcap > 0.f ? 1.4426950408889634f : scale_log2;
+  const float cap_in = softcap > 0.f ? scale_log2 * (2.0f / softcap) : 0.f;      // s -> 2 log2(e) s scale / c
   const int* bt = block_tables + (int64_t)b * bt_stride;
 
   if (threadIdx.x == 0) {
@@ -439,7 +452,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     int first_row = -1;
     if (lane < boxes) {
       const int j0 = kt + pg * page_size;
-      if (j0 < hi && j0 + page_size > lo_seen) {
+      if (j0 < hi && (j0 + page_size > lo_seen || (EXTRA && j0 < keep_first))) {
         const int page = bt[j0 / page_size];
         if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size + row_off;
       }
@@ -447,7 +460,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     return first_row;
   };
   int first_row_0 = -1;
-  if (warp == 0 || warp == 10) first_row_0 = first_row_of(lo);
+  if (warp == 0 || warp == 10) first_row_0 = first_row_of(tile_start(0));
   pdl_wait();
   bool ok = true;
 
@@ -466,7 +479,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     unsigned long long* const full = is_v ? v_full : k_full;
     unsigned long long* const empty = is_v ? v_empty : k_empty;
     for (int it = 0; it < n_tiles && ok; ++it) {
-      const int s = it % RING, kt = lo + it * KEYS;
+      const int s = it % RING, kt = tile_start(it);
       ok = tma::mbar_wait(&empty[s], ((it / RING) & 1) ^ 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -532,26 +545,28 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     const float neg_inf = -INFINITY;
     float m_mine = neg_inf, l = 0.f;                       // l: the sum over this group's tiles, relative to m_mine
     // the keys this row sees: j_min .. j_max (none for a row beyond the tile's tokens)
-    const int j_max = row_ok ? pos : -(1 << 30), j_min = window > 0 ? pos - window + 1 : -(1 << 30);
+    const int j_max = row_ok ? pos : -(1 << 30);
+    const int j_min = window > 0 ? pos - window + 1 : (chunk > 0 ? (pos / chunk) * chunk : -(1 << 30));
+    const int chunk_hi = chunk > 0 ? (p_hi / chunk) * chunk : 0;
     // Both groups run every named barrier of every tile, also after a wait has given up (ok == false): then only
     // the work is skipped, so no warp is left waiting for a partner that has gone.
     for (int it = g; it < n_tiles; it += 2) {
-      const int kt = lo + it * KEYS;
+      const int kt = tile_start(it);
       const uint32_t t_s = tmem_s + (it % 3) * KEYS + t_row;
-      const bool need_mask = kt + KEYS - 1 > p_lo || (window > 0 && kt <= p_hi - window) || n_tok * gp < TA_ROWS;
+      const bool need_mask = kt + KEYS - 1 > p_lo || (window > 0 && kt <= p_hi - window) || (EXTRA && kt < chunk_hi) || n_tok * gp < TA_ROWS;
       // Q K^T (it) was issued after Q K^T (it - 3), which this group's last tile (it - 2) waited for in its turn.
       if (ok) ok = tma::mbar_wait(&s_ready[it % 3], (it / 3) & 1);
       ok = __all_sync(0xffffffffu, ok);
       float mx = neg_inf;
-      const int c_min = j_min - kt, c_max = j_max - kt;      // the same as columns of this tile
-      auto seen = [&](int col) { return col >= c_min && col <= c_max; };
+      const int c_min = j_min - kt, c_max = j_max - kt, c_keep = keep_first - kt;      // the same as columns of this tile
+      auto seen = [&](int col) { return col <= c_max && (col >= c_min || (EXTRA && col < c_keep)); };
       // A masked tile by pieces of 32 columns: the rows of a warp are consecutive tokens (of one or two heads), so
       // most pieces are seen whole, or not at all, by the whole warp; only the others are tested column by column.
       // 0: all rows of the warp see all of the piece, 1: none sees any of it, 2: mixed.
       auto piece_kind = [&](int c0) {
         if (!need_mask) return 0;
-        if (__all_sync(0xffffffffu, c_min <= c0 && c_max >= c0 + 31)) return 0;
-        if (__all_sync(0xffffffffu, c_max < c0 || c_min > c0 + 31)) return 1;
+        if (__all_sync(0xffffffffu, c_max >= c0 + 31 && (c_min <= c0 || (EXTRA && c_keep >= c0 + 32)))) return 0;
+        if (__all_sync(0xffffffffu, c_max < c0 || (c_min > c0 + 31 && (!EXTRA || c_keep <= c0)))) return 1;
         return 2;
       };
       // The thread's whole row of S, 128 scores, stays in registers from the maximum to the exponentials: tensor
@@ -571,12 +586,19 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
               if (seen(c0 + jj)) mx = fmaxf(mx, sv[jj]);
           }
         };
+        // c tanh(x) = c (1 - 2 / (1 + 2^(2 log2(e) x)))
+        auto cap_half = [&](float (&half)[64]) {
+#pragma unroll
+          for (int jj = 0; jj < 64; ++jj) half[jj] = softcap - 2.0f * softcap * __frcp_rn(1.0f + ex2(half[jj] * cap_in));
+        };
         tc5::ld_64cols(t_s, s_lo);
         tc5::wait_ld();
         tc5::ld_64cols(t_s + 64, s_hi);                      // on its way while the first half is worked on
+        if (softcap > 0.f) cap_half(s_lo);
         piece_max(piece(s_lo, 0), 0);
         piece_max(piece(s_lo, 1), 32);
         tc5::wait_ld();
+        if (softcap > 0.f) cap_half(s_hi);
         piece_max(piece(s_hi, 0), 64);
         piece_max(piece(s_hi, 1), 96);
       }
@@ -586,14 +608,14 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
         asm volatile("bar.sync %0, 256;\n" ::"r"(2 + ((it - 1) & 1)) : "memory");
         m_prev = ref_m[(it - 1) & 1][r];
       }
-      const bool raise = ok && mx > neg_inf && (m_prev == neg_inf || (mx - m_prev) * scale_log2 > 8.0f);
+      const bool raise = ok && mx > neg_inf && (m_prev == neg_inf || (mx - m_prev) * sl2 > 8.0f);
       const float m_new = raise ? mx : m_prev;
       ref_m[it & 1][r] = m_new;
       __threadfence_block();
       asm volatile("bar.arrive %0, 256;\n" ::"r"(2 + (it & 1)) : "memory");
       if (ok) {
         if (m_new != m_mine) {                               // m_mine = -inf: nothing summed yet
-          l *= ex2((m_mine - m_new) * scale_log2);
+          l *= ex2((m_mine - m_new) * sl2);
           m_mine = m_new;
         }
         if (it > 0 && __any_sync(0xffffffffu, raise)) {
@@ -602,7 +624,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
           ok = tma::mbar_wait(&o_ready[(it - 1) & 1], ((it - 1) >> 1) & 1);
           if (ok) {
             tc5::fence_after_sync();
-            const float alpha = raise ? ex2((m_prev - m_new) * scale_log2) : 1.f;      // m_prev = -inf gives 0
+            const float alpha = raise ? ex2((m_prev - m_new) * sl2) : 1.f;      // m_prev = -inf gives 0
 #pragma unroll
             for (int c0 = 0; c0 < HD; c0 += 16) {             // (a rare path: small pieces, the row of S is held meanwhile)
               float v[16];
@@ -621,7 +643,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
         // before this one into the buffer, V (it - 3), is over: P V (it - 3) was issued before Q K^T (it).
         if (ok) ok = tma::mbar_wait(&v_full[it % RING], (it / RING) & 1);
         const int j = kt + r;
-        if (ok && (j >= hi || j < lo_seen)) {
+        if (ok && (j >= hi || (j < lo_seen && (!EXTRA || j >= keep_first)))) {
 #pragma unroll
           for (int hf = 0; hf < HALVES; ++hf) {
             uint4* row = reinterpret_cast<uint4*>(v_s + (it % RING) * KV_BYTES + hf * KB_BYTES + r * 128);
@@ -632,7 +654,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
       }
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
-        const float mu_s = (m_new == neg_inf ? 0.f : m_new) * scale_log2;
+        const float mu_s = (m_new == neg_inf ? 0.f : m_new) * sl2;
         // p = 2^(s * scale - reference * scale), 0 for a key the row does not see (its score is set to -inf), rounded
         // to bfloat16: keys c .. c+31 of the row go to columns c / 2 .. c / 2 + 15 of the S buffer, which are read already.
         auto piece_of_p = [&](float (&sv)[32], int c) {
@@ -649,7 +671,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
             }
 #pragma unroll
             for (int jj = 0; jj < 32; jj += 2) {
-              const float p0 = ex2(fmaf(sv[jj], scale_log2, -mu_s)), p1 = ex2(fmaf(sv[jj + 1], scale_log2, -mu_s));
+              const float p0 = ex2(fmaf(sv[jj], sl2, -mu_s)), p1 = ex2(fmaf(sv[jj + 1], sl2, -mu_s));
               l += p0 + p1;
               __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
               pk[jj >> 1] = *reinterpret_cast<uint32_t*>(&h2);
@@ -675,10 +697,11 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     // The two groups' sums meet in the first K buffer: every Q K^T is over (the group of the last tile waited for
     // its S, and both groups have met since), and the block's shared memory has no room to spare.
     float* l_part = reinterpret_cast<float*>(k_s);
-    l_part[g * TA_ROWS + r] = m_mine == neg_inf ? 0.f : l * ex2((m_mine - m_fin) * scale_log2);
+    l_part[g * TA_ROWS + r] = m_mine == neg_inf ? 0.f : l * ex2((m_mine - m_fin) * sl2);
     asm volatile("bar.sync 1, 256;\n" ::: "memory");
     l = l_part[r] + l_part[TA_ROWS + r];
-    if (sink) l += ex2(-m_fin * scale_log2);                 // a key of score 0 that has no value
+    if (sinks) l += ex2(fmaf(sinks[head0 + r / tq], 1.4426950408889634f, -(m_fin == neg_inf ? 0.f : m_fin) * sl2));   // a learned score
+    else if (sink) l += ex2(-m_fin * scale_log2);            // a key of score 0 that has no value
     // The last P V.  The phase before it on that barrier is P V (n - 3), which nothing so far has waited for: Q K^T
     // (n - 1) was issued after P V (n - 4) only, the phase before P V (n - 2) on the other barrier.  So that one first
     // (the group of the last tile waited for S (n - 1), and both groups have met since); the products end in order.
@@ -742,13 +765,15 @@ template <int HD, int KT, bool TWO_GROUPS>
 int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride, const int* block_tables, int bt_stride,
               const int* cu_seqlens, const int* context_lens, const int* tiles, int num_tiles, int nh, int nkv, int gp,
               int page_size, float scale, int window, int sink, const float* gate, int64_t gate_stride, int* err,
-              cudaStream_t stream) {
+              int keep_first, int chunk, float softcap, const float* sinks, cudaStream_t stream) {
   const size_t smem = TWO_GROUPS ? (size_t)TA_ROWS * HD * 2 + 6 * (size_t)KT * HD * 2 + 1024
                                  : (size_t)TA_ROWS * HD * 2 + 4 * (size_t)KT * HD * 2 + 2 * (size_t)TA_ROWS * KT * 2 + 1024;
-  auto kernel = TWO_GROUPS ? attn_prefill_tcgen05_two_groups_kernel<HD> : attn_prefill_tcgen05_kernel<HD, KT>;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = TWO_GROUPS ? cudaFuncSetAttribute(attn_prefill_tcgen05_two_groups_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                               : cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<HD, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (TWO_GROUPS && e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_prefill_tcgen05_two_groups_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ME_REQUIRE(e == cudaSuccess, "me_attn_prefill_tcgen05: cannot raise shared memory: %s", cudaGetErrorString(e));
     attr_set = true;
   }
@@ -756,9 +781,17 @@ int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_
   // (Tiles fastest, so that the blocks of a round share one or two heads' keys in L2, measured the same at 16,384 tokens
   // and 16% slower at 2,048, where the last round then holds long tiles.)
   dim3 grid(nkv * (nh / nkv / gp), num_tiles);
-  me_launch(kernel, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
-            *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
-            context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, sink, gate, gate_stride, err);
+  if constexpr (TWO_GROUPS) {
+    auto kernel = (keep_first > 0 || chunk > 0 || softcap > 0.f || sinks) ? attn_prefill_tcgen05_two_groups_kernel<HD, true>
+                                                                          : attn_prefill_tcgen05_two_groups_kernel<HD, false>;
+    me_launch(kernel, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
+              *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
+              context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, sink, gate, gate_stride, err,
+              keep_first, chunk, softcap, sinks);
+  } else
+    me_launch(attn_prefill_tcgen05_kernel<HD, KT>, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
+              *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
+              context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, sink, gate, gate_stride, err);
   return 0;
 }
 
@@ -778,12 +811,15 @@ ME_API int me_attn_prefill_tcgen05_heads_per_block(int nh, int nkv, int hd, int 
 // slot as [pages * 2 * kv_heads * page_size][head_dim], boxes page_size x 64; both with the 128-byte swizzle.
 // ``tiles``: (request, first local query) per block, each covering 128 / heads-per-block query tokens.
 // ``sink``: the softmax's denominator has one more term, exp(0) (a key of score 0 without a value).  ``gate``: float32 rows of
-// nh * head_dim pre-activations (or null): the output is multiplied by their sigmoid.
+// nh * head_dim pre-activations (or null): the output is multiplied by their sigmoid.  ``keep_first``: the window also shows
+// keys j < keep_first.  ``chunk`` (instead of a window): a query at p sees the keys j <= p from floor(p / chunk) * chunk on.
+// ``softcap`` c: scores become c tanh(score * scale / c).  ``sinks``: float32 [nh], the extra term is exp(sinks[head]),
+// neither scaled nor capped.  These four are the kernel with two groups' alone.
 ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride,
                                    const int* block_tables, int bt_stride, const int* cu_seqlens, const int* context_lens,
                                    const int* tiles, int num_tiles, int nh, int nkv, int hd, int page_size, float scale,
                                    int window, int key_tile, int sink, const float* gate, int64_t gate_stride, int* err,
-                                   cudaStream_t stream) {
+                                   int keep_first, int chunk, float softcap, const float* sinks, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   const int gp = me_attn_prefill_tcgen05_heads_per_block(nh, nkv, hd, page_size);
   ME_REQUIRE(gp > 0, "me_attn_prefill_tcgen05: head_dim %d, %d/%d heads, pages of %d are not taken", hd, nh, nkv, page_size);
@@ -793,11 +829,15 @@ ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* 
   // key_tile: keys per step of the loop.  128 (and 0): the kernel with two softmax groups and P in tensor memory, the
   // faster one; 64: the kernel with one group and P in shared memory, which needs less of both memories.
   if (key_tile == 0) key_tile = 128;
+  ME_REQUIRE(key_tile == 128 || (keep_first == 0 && chunk == 0 && softcap == 0.f && sinks == nullptr),
+             "me_attn_prefill_tcgen05: kept first keys, chunks, capped scores and learned sinks need the key tile of 128");
+  ME_REQUIRE(keep_first >= 0 && chunk >= 0 && softcap >= 0.f && !(chunk > 0 && window > 0) && (keep_first == 0 || window > 0),
+             "me_attn_prefill_tcgen05: a window (with kept first keys) or chunks, not both");
   ME_REQUIRE((key_tile == 64 || key_tile == 128) && key_tile % page_size == 0, "me_attn_prefill_tcgen05: key tile %d with pages of %d",
              key_tile, page_size);
   int rc;
 #define ME_TA_ARGS q_map, kv_map, out, out_row_stride, block_tables, bt_stride, cu_seqlens, context_lens, tiles, num_tiles, nh, nkv, gp, \
-                   page_size, scale, window, sink, gate, gate_stride, err, stream
+                   page_size, scale, window, sink, gate, gate_stride, err, keep_first, chunk, softcap, sinks, stream
   if (hd == 64) rc = key_tile == 64 ? launch_ta<64, 64, false>(ME_TA_ARGS) : launch_ta<64, 128, true>(ME_TA_ARGS);
   else rc = key_tile == 64 ? launch_ta<128, 64, false>(ME_TA_ARGS) : launch_ta<128, 128, true>(ME_TA_ARGS);
 #undef ME_TA_ARGS

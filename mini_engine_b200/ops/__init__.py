@@ -39,7 +39,7 @@ _PROTOS = {
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _I, _P, _L, _P],
+    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _I, _P, _L, _I, _I, _F, _P, _P],
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _I, _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _F, _F, _F, _P],
@@ -47,7 +47,7 @@ _PROTOS = {
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_shared": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
-    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _L, _P, _P],
+    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _L, _P, _I, _I, _F, _P, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
@@ -60,7 +60,7 @@ _PROTOS = {
     "me_parallel_norm": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "me_attn_prep": [_P, _L, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_gla_decay": [_P, _L, _I, _I, _P, _I, _P, _F, _P, _I, _I, _P],
-    "me_gla_scan": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "me_gla_scan": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P],
     "me_activation": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _P],
     "me_soft_cap": [_P, _L, _F, _P],
     "me_add_row_vector": [_P, _I, _I, _I, _P, _P],
@@ -98,7 +98,7 @@ def require_extension() -> ctypes.CDLL:
         fn.argtypes = args
         fn.restype = ctypes.c_int
     if (lib.me_attn_chunk_tile_q() != ATTN_TILE_Q or lib.me_attn_decode_partition() != DECODE_PARTITION
-            or lib.me_sink_attn_tile_q() != SINK_ATTN_TILE_Q):
+            or lib.me_sink_attn_tile_q() != SINK_ATTN_TILE_Q or lib.me_gla_chunk_len() != GLA_CHUNK):
         raise KernelError("the kernel library and ops/__init__.py disagree on tile sizes")
     lib.me_attn_prefill_heads_per_block.argtypes = [_I, _I, _I]
     lib.me_attn_prefill_tcgen05_heads_per_block.argtypes = [_I, _I, _I, _I]
@@ -844,10 +844,14 @@ def prefill_tcgen05_heads_per_block(num_heads: int, num_kv_heads: int, head_dim:
 
 def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
                               scale, window, tiles=None, num_tiles=None, key_tile: int = 0, sink: bool = False,
-                              gate: Optional[torch.Tensor] = None) -> None:
+                              gate: Optional[torch.Tensor] = None, keep_first: int = 0, chunk: int = 0, softcap: float = 0.0,
+                              sinks: Optional[torch.Tensor] = None) -> None:
     """The tcgen05 / tensor-memory prefill kernel (bfloat16, head_dim 64 or 128, page sizes dividing 128) over
     tiles of 128 / heads-per-block tokens; Q, K and V arrive by tensor-map loads.  ``sink``: one more term, exp(0), in
-    the softmax's denominator; ``gate``: float32 rows of pre-activations whose sigmoid multiplies the output."""
+    the softmax's denominator; ``gate``: float32 rows of pre-activations whose sigmoid multiplies the output.
+    ``keep_first``: the window also shows the keys j < keep_first; ``chunk`` (instead of a window): the keys of the query's
+    own chunk; ``softcap`` c: scores become c tanh(s / c) after the scale; ``sinks`` (float32 [heads]): the extra term is
+    exp(sinks[head]) (the kernel with the key tile of 128 only)."""
     gp = prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, head_dim, page_size)
     _need(gp > 0 and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.data_ptr() % 16 == 0,
           "attention_prefill_tcgen05: shape or dtype not taken by the kernel")
@@ -858,17 +862,19 @@ def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool,
           out.stride(0), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), tiles.data_ptr(), num_tiles, num_heads, num_kv_heads, head_dim, page_size,
           float(scale), int(window or 0), key_tile, 1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
-          meta.error_flag.data_ptr(), _stream())
+          meta.error_flag.data_ptr(), int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), _ptr(sinks), _stream())
 
 
 use_tcgen05_attention = True   # False: portions of prompts use the mma.sync kernel instead (a switch for comparisons)
 
 
 def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
-                     scale, window, kind: str = "auto", sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
+                     scale, window, kind: str = "auto", sink: bool = False, gate: Optional[torch.Tensor] = None,
+                     keep_first: int = 0, chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None) -> None:
     """The split-K decode kernel and its merge over requests [0, meta.num_decodes).  ``sink``: one more term, exp(0), in
     the softmax's denominator (added once, in the merge); ``gate``: float32 rows of pre-activations whose sigmoid
-    multiplies the output.
+    multiplies the output.  ``sinks`` (float32 [heads]): the term is exp(sinks[head]).  ``keep_first``, ``chunk`` and
+    ``softcap`` as for ``attention_prefill_tcgen05`` (the partition kernel fed by tensor-map loads only).
 
     ``kind`` picks the partition kernel: "auto" (for bfloat16 with head_dim 64 or 128 the tensor cores, fed by
     tensor-map loads where the page size divides 128, else by cp.async; otherwise the CUDA cores), or one
@@ -884,7 +890,8 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
           meta.context_lens.data_ptr(), D, num_heads, num_kv_heads, head_dim, page_size, float(scale),
           int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts,
           _ptr(meta.error_flag), DECODE_KINDS[kind], tm.ptr if tm is not None else 0, 1 if sink else 0, _ptr(gate),
-          gate.stride(0) if gate is not None else 0, _stream())
+          gate.stride(0) if gate is not None else 0, int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), _ptr(sinks),
+          _stream())
     global launches
     launches += 1          # partition kernel + merge kernel
 
@@ -1139,19 +1146,29 @@ def gla_decay(proj: torch.Tensor, off_a1: int, rank: int, w2: torch.Tensor, bias
 gla_chunks = True     # portions of prompts run the recurrence a chunk of tokens at a time; a switch for comparisons
 
 
+GLA_CHUNK = 64        # tokens that the chunk kernels of csrc/gla.cu take at a time (a tile list of this size must exist)
+
+
 def gla_scan(proj: torch.Tensor, offsets: dict, la: torch.Tensor, S: torch.Tensor, meta, state_slots: torch.Tensor, o: torch.Tensor,
-             num_heads: int, dim: int, vdim: int, q_scale: float) -> None:
+             num_heads: int, dim: int, vdim: int, q_scale: float, scores: Optional[torch.Tensor] = None) -> None:
     """Walks every request's tokens of this step through S_t = diag(exp(la_t)) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t from the
     state in its slot (see csrc/gla.cu).  ``proj`` [T, N] float32 holds q, k, v at the column ``offsets``; ``la`` [T, heads * dim]
-    and ``o`` [T, heads * vdim] float32."""
+    and ``o`` [T, heads * vdim] float32.  With ``scores`` ([T, heads, GLA_CHUNK] float32 workspace) the requests that bring
+    several tokens take GLA_CHUNK tokens at a time (``gla_chunks``); ``la`` is overwritten on the way."""
     T = proj.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "gla_scan: projections must be float32 rows")
     _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (S, la, o)), "gla_scan: float32 state, decays and output")
     _need(tuple(S.shape[1:]) == (num_heads, dim, vdim) and tuple(la.shape) == (T, num_heads * dim)
           and tuple(o.shape) == (T, num_heads * vdim), "gla_scan: shapes")
+    tiles, n_tiles = meta.tile_lists[GLA_CHUNK]
+    chunked = gla_chunks and scores is not None and n_tiles > 0
+    if chunked:
+        _need(scores.dtype == torch.float32 and scores.is_contiguous() and scores.numel() >= T * num_heads * GLA_CHUNK,
+              "gla_scan: the workspace of scores is float32 [T, heads, GLA_CHUNK]")
     _call("me_gla_scan", proj.data_ptr(), proj.stride(0), offsets["q"], offsets["k"], offsets["v"], la.data_ptr(), S.data_ptr(),
           meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), state_slots.data_ptr(), o.data_ptr(), meta.num_reqs,
-          num_heads, dim, vdim, float(q_scale), 1 if (gla_chunks and T > meta.num_reqs) else 0, _stream())
+          num_heads, dim, vdim, float(q_scale), tiles.data_ptr() if chunked else 0, n_tiles if chunked else 0, meta.num_decodes,
+          scores.data_ptr() if chunked else 0, _stream())
 
 
 # ---- attention through a latent --------------------------------------------------------------------
@@ -1416,16 +1433,18 @@ def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
     _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == num_heads and sinks.is_contiguous()),
           "sink_attention: learned sinks are float32 [heads]")
     _need(not (chunk and window), "sink_attention: a window or chunks, not both")
-    plain = sinks is None and not softcap and not keep_first and not chunk      # what the tensor-core kernels know
+    masked = bool(softcap or keep_first or chunk)      # what only the kernels fed by tensor-map loads know
     decodes, tiles_left = meta.num_decodes, True
-    fast = (plain and use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
+    fast = (use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
             and meta.error_flag is not None and q.is_contiguous() and q.data_ptr() % 16 == 0)
-    if fast and decodes:
-        attention_decode(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window, sink=sink, gate=gate)
+    extras = dict(keep_first=keep_first, chunk=chunk or 0, softcap=softcap or 0.0, sinks=sinks)
+    if fast and decodes and (not masked or (page_size >= 8 and DECODE_PARTITION % page_size == 0)):
+        attention_decode(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window, sink=sink, gate=gate,
+                         **extras)
         decodes = 0
     if fast and meta.num_tiles > 0 and use_tcgen05_attention and prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, HD, page_size) > 0:
         attention_prefill_tcgen05(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window,
-                                  sink=sink, gate=gate)
+                                  sink=sink, gate=gate, **extras)
         tiles_left = False
     tiles, n_tiles = meta.tile_lists[SINK_ATTN_TILE_Q]
     if not tiles_left:

@@ -19,8 +19,9 @@ TOL = {"float32": 3e-5, "bfloat16": 1e-1}
 MEAN_TOL = {"float32": 1e-5, "bfloat16": 3e-2}
 # In bfloat16 a router's close call may go the other way (the random weights here take no care to keep the chosen logits
 # apart): that token then runs another expert and is off by tens of per cent, alone.  A model with routers may have a few
-# such positions; in float32, and in a model whose routers take every expert, there is none.
-FLIPS = {"float32": 0.0, "bfloat16": 0.03}
+# such positions, in proportion to the router decisions a token meets on its way (a looped layer decides once a pass); in
+# float32, and in a model whose routers take every expert, there is none.
+FLIPS = {"float32": 0.0, "bfloat16": 0.015}
 _plain = {}
 
 
@@ -55,7 +56,11 @@ def _replay(name, dtype, steps, max_tokens=None, folder=None, **kw):
 
 
 def _routed(cfg):
-    return any(l["mlp"] and l["mlp"]["kind"] == "moe" and l["mlp"]["router"]["top"] < l["mlp"]["router"]["experts"] for l in cfg["layers"])
+    """How many times a token passes a router that has a choice to make."""
+    loop = cfg.get("loop") or {"start": 0, "stop": 0, "times": 1}
+    runs = [loop["times"] if loop["start"] <= i < loop["stop"] else 1 for i in range(len(cfg["layers"]))]
+    return sum(n for n, l in zip(runs, cfg["layers"])
+               if l["mlp"] and l["mlp"]["kind"] == "moe" and l["mlp"]["router"]["top"] < l["mlp"]["router"]["experts"])
 
 
 def _check(name, dtype, reqs, got, tag, folder=None, cfg=None):
@@ -65,9 +70,10 @@ def _check(name, dtype, reqs, got, tag, folder=None, cfg=None):
         assert mine.shape == ref.shape and np.isfinite(mine).all()
         err = _error(mine, ref)
         bad = np.nonzero(err > TOL[dtype])[0]
-        allowed = max(1, int(FLIPS[dtype] * len(r))) if _routed(cfg) and FLIPS[dtype] else 0
+        allowed = max(1, int(np.ceil(FLIPS[dtype] * len(r) * _routed(cfg)))) if _routed(cfg) and FLIPS[dtype] else 0
         assert bad.size <= allowed, (f"model {name} {dtype} cutting {tag!r} request {i}: first wrong token at position {bad[0]} "
-                                     f"(error {err[bad[0]]:.3e}, tolerance {TOL[dtype]})")
+                                     f"(error {err[bad[0]]:.3e}, tolerance {TOL[dtype]}); all: "
+                                     + ", ".join(f"{p}: {err[p]:.2e}" for p in bad[:12]) + f"; median {np.median(err):.2e}")
         assert np.median(err) < MEAN_TOL[dtype] and err.mean() < 3 * MEAN_TOL[dtype], f"model {name} {dtype} cutting {tag!r} request {i}: mean error {err.mean():.3e}"
 
 
