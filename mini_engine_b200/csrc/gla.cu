@@ -10,30 +10,43 @@
 //   me_gla_scan   walks a request's tokens of this step in order from the state its slot holds (from zero when the
 //                 portion starts at position 0) and leaves the new state there; a token's result does not depend on where
 //                 the sequence was cut beyond the order of sums.  One block = one request x one head x GLA_VB columns of S.
-//                 Portions of prompts take GLA_LC tokens at a time (see gla_chunk_kernel).
+//                 Portions of prompts take GLA_LC tokens at a time (see gla_intra_kernel and the three kernels behind it).
 #include "common.cuh"
 
 constexpr int GLA_VB = 16, GLA_DY = 16, GLA_THREADS = GLA_VB * GLA_DY;
 
 __device__ __forceinline__ float gla_log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// la[t, c] = logsigmoid(b[c] + sum_r W2[c, r] a1[t, r]) * inv_tau.  One block = one token x 256 channels.
+// la[t, c] = logsigmoid(b[c] + sum_r W2[c, r] a1[t, r]) * inv_tau.  One block = GLA_DT tokens x 128 channels: a thread
+// reads its channel's row of W2 once for all of the block's tokens.
+constexpr int GLA_DT = 8;
+
 template <typename TW>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 gla_decay_kernel(const float* __restrict__ proj, int64_t ld, int off_a1, int rank, const TW* __restrict__ w2,
-                 const float* __restrict__ bias, float inv_tau, float* __restrict__ la, int C) {
-  extern __shared__ float a1[];
+                 const float* __restrict__ bias, float inv_tau, float* __restrict__ la, int T, int C) {
+  extern __shared__ float a1[];                 // [GLA_DT][rank]
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  for (int r = threadIdx.x; r < rank; r += blockDim.x) a1[r] = proj[(int64_t)t * ld + off_a1 + r];
+  const int t0 = blockIdx.x * GLA_DT;
+  for (int i = threadIdx.x; i < GLA_DT * rank; i += blockDim.x) {
+    const int t = i / rank, r = i - t * rank;
+    a1[i] = t0 + t < T ? proj[(int64_t)(t0 + t) * ld + off_a1 + r] : 0.f;
+  }
   __syncthreads();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
   const TW* w = w2 + (int64_t)c * rank;
-  float z = 0.f;
-  for (int r = 0; r < rank; ++r) z = fmaf(to_f<TW>(w[r]), a1[r], z);
-  la[(int64_t)t * C + c] = gla_log_sigmoid(z + bias[c]) * inv_tau;
+  float z[GLA_DT] = {};
+  for (int r = 0; r < rank; ++r) {
+    const float wr = to_f<TW>(w[r]);
+#pragma unroll
+    for (int t = 0; t < GLA_DT; ++t) z[t] = fmaf(wr, a1[t * rank + r], z[t]);
+  }
+  const float bc = bias[c];
+#pragma unroll
+  for (int t = 0; t < GLA_DT; ++t)
+    if (t0 + t < T) la[(int64_t)(t0 + t) * C + c] = gla_log_sigmoid(z[t] + bc) * inv_tau;
 }
 
 __global__ void __launch_bounds__(GLA_THREADS)
@@ -94,9 +107,9 @@ gla_scan_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_k
 //   S_L = diag(exp(B_L)) S0 + sum_s (k_s * exp(B_L - B_s)) v_s^T
 // Every exponent is <= 0 (decays lie in (0, 1]), whatever the decays are: nothing is divided by a decay.  A does not depend
 // on the state, so gla_intra_kernel computes it for all chunks of a step at once (one block = one chunk x one head) and leaves
-// it, with B, in global memory; gla_chunk_kernel then walks a request's chunks in order with two dense float32 products a
-// chunk.  B is held in units of log 2 (exp2f).  float32 throughout; the results differ from the token-by-token kernel by the
-// order of the sums only.
+// it, with B, in global memory; the kernels further down form the other products and walk the state from chunk to chunk.
+// B is held in units of log 2 (exp2f).  float32 throughout; the results differ from the token-by-token kernel by the order
+// of the sums only.
 constexpr int GLA_LC = 64;
 constexpr float GLA_LOG2E = 1.4426950408889634f;
 
@@ -120,18 +133,16 @@ gla_intra_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_
   const int tok0 = cu_seqlens[b] + q0;
   const int L = min(LC, cu_seqlens[b + 1] - tok0);
   if (L <= 0) return;
+  // the fill loads from clamped places and selects afterwards, so that the loads of several turns are in flight together
+#pragma unroll 4
   for (int idx = tid; idx < LC * D; idx += 256) {
     const int t = idx / D, d = idx - t * D;
-    float qv = 0.f, kv = 0.f, bv = 0.f;
-    if (t < L) {
-      const float* row = proj + (int64_t)(tok0 + t) * ld;
-      qv = row[off_q + hd * D + d] * q_scale;
-      kv = row[off_k + hd * D + d];
-      bv = la[(int64_t)(tok0 + t) * H * D + hd * D + d] * GLA_LOG2E;
-    }
-    Qc[t * ldq + d] = qv;
-    Kc[t * ldq + d] = kv;
-    Bc[t * ldq + d] = bv;
+    const float* row = proj + (int64_t)(tok0 + min(t, L - 1)) * ld;
+    const float qv = row[off_q + hd * D + d] * q_scale, kv = row[off_k + hd * D + d];
+    const float bv = la[(int64_t)(tok0 + min(t, L - 1)) * H * D + hd * D + d] * GLA_LOG2E;
+    Qc[t * ldq + d] = t < L ? qv : 0.f;
+    Kc[t * ldq + d] = t < L ? kv : 0.f;
+    Bc[t * ldq + d] = t < L ? bv : 0.f;
   }
   __syncthreads();
   for (int d = tid; d < D; d += 256) {          // the inclusive sums, a channel a thread
@@ -176,102 +187,196 @@ gla_intra_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_
   }
 }
 
-// One block = one request (first_req + blockIdx.x) x one head x GLA_VB columns of S.  bsum and A are gla_intra_kernel's.
-template <int MAXD>
-__global__ void __launch_bounds__(GLA_THREADS)
-gla_chunk_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_k, int off_v, const float* __restrict__ bsum,
-                 const float* __restrict__ A, float* __restrict__ S_state, const int* __restrict__ cu_seqlens,
-                 const int* __restrict__ context_lens, const int* __restrict__ state_slots, float* __restrict__ o, int first_req,
-                 int H, int D, int V, float q_scale) {
+// The three kernels behind gla_intra_kernel.  Only the state's walk from chunk to chunk is sequential, and that is one
+// multiply-add an element a chunk; the two products of every chunk run for all chunks of the step at once.
+//   gla_chunk_state_kernel   U_c = sum_s (k_s * exp(B_L - B_s)) v_s^T of every chunk c, into states[c]
+//   gla_state_walk_kernel    per request, in order: states[c] <- the state in front of chunk c; S <- diag(exp(B_L)) S + U_c;
+//                            the last S goes to the request's slot
+//   gla_chunk_out_kernel     o_t = [q_t * exp(B_t) | A[t][.]] [states[c]; v] of every chunk: one product over D + GLA_LC terms
+// states: [n_tiles, H, D, V] float32.  The first two kernels and the third take GLA_VT columns of S a block, 4 x 4 results a
+// thread.
+constexpr int GLA_VT = 64;
+
+// One block = one chunk x one head x GLA_VT columns.  bsum: gla_intra_kernel's inclusive sums (units of log 2).
+__global__ void __launch_bounds__(256)
+gla_chunk_state_kernel(const float* __restrict__ proj, int64_t ld, int off_k, int off_v, const float* __restrict__ bsum,
+                       const int* __restrict__ cu_seqlens, const int* __restrict__ tiles, float* __restrict__ states, int H, int D,
+                       int V) {
   extern __shared__ float smem[];
-  constexpr int LC = GLA_LC, VB = GLA_VB;
-  const int ldq = D + 1;
-  float* S = smem;                              // [D][VB + 1]
-  float* Qt = S + D * (VB + 1);                 // [LC][D + 1]   q_t * exp(B_t)
-  float* Kt = Qt + LC * ldq;                    // [LC][D + 1]   k_s * exp(B_L - B_s)
-  float* Vc = Kt + LC * ldq;                    // [LC][VB + 1]
-  float* Ac = Vc + LC * (VB + 1);               // [LC][LC + 1]
-  float* bL = Ac + LC * (LC + 1);               // [D]  B_L, then exp(B_L)
-  const int b = first_req + blockIdx.x, hd = blockIdx.y, v0 = blockIdx.z * VB;
-  const int tid = threadIdx.x, vc = tid % VB, dy = tid / VB;
-  const bool v_ok = v0 + vc < V;
+  constexpr int LC = GLA_LC, VT = GLA_VT;
+  const int Dp = (D + 63) / 64 * 64, ldk = Dp + 1;
+  float* Kt = smem;                             // [LC][Dp + 1]   k_s * exp(B_L - B_s); zero beyond L and D
+  float* Vc = Kt + LC * ldk;                    // [LC][VT]
+  const int tid = threadIdx.x, hd = blockIdx.y, v0 = blockIdx.z * VT;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
+  const int tok0 = cu_seqlens[b] + q0;
+  const int L = min(LC, cu_seqlens[b + 1] - tok0);
+  if (L <= 0) return;
+  const float* bl = bsum + (int64_t)(tok0 + L - 1) * H * D + hd * D;
+  // the fills load from clamped places and select afterwards, so that the loads of several turns are in flight together
+#pragma unroll 8
+  for (int idx = tid; idx < LC * Dp; idx += 256) {
+    const int t = idx / Dp, d = idx - t * Dp;
+    const int tc = min(t, L - 1), dc = min(d, D - 1);
+    const float kv = proj[(int64_t)(tok0 + tc) * ld + off_k + hd * D + dc] *
+                     exp2f(bl[dc] - bsum[(int64_t)(tok0 + tc) * H * D + hd * D + dc]);
+    Kt[t * ldk + d] = (t < L && d < D) ? kv : 0.f;
+  }
+#pragma unroll 8
+  for (int idx = tid; idx < LC * VT; idx += 256) {
+    const int t = idx / VT, v = idx - t * VT;
+    const float x = proj[(int64_t)(tok0 + min(t, L - 1)) * ld + off_v + hd * V + min(v0 + v, V - 1)];
+    Vc[idx] = (t < L && v0 + v < V) ? x : 0.f;
+  }
+  __syncthreads();
+  const int ty = tid / 16, tx = tid % 16;
+  float* out = states + ((int64_t)blockIdx.x * H + hd) * D * V;
+  for (int d0 = 0; d0 < D; d0 += 64) {
+    float acc[4][4] = {};
+    for (int s = 0; s < L; ++s) {
+      float kk[4], vv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) kk[i] = Kt[s * ldk + d0 + ty + 16 * i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) vv[j] = Vc[s * VT + tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(kk[i], vv[j], acc[i][j]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int d = d0 + ty + 16 * i;
+      if (d >= D) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int v = v0 + tx + 16 * j;
+        if (v < V) out[(int64_t)d * V + v] = acc[i][j];
+      }
+    }
+  }
+}
+
+// One block = one request (first_req + blockIdx.x) x one head x 256 elements of S.  The loads of a chunk do not wait for the
+// chunk before; only the multiply-add does.
+__global__ void __launch_bounds__(256)
+gla_state_walk_kernel(const float* __restrict__ bsum, float* __restrict__ states, float* __restrict__ S_state,
+                      const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens, const int* __restrict__ state_slots,
+                      const int* __restrict__ tiles, int n_tiles, int first_req, int H, int D, int V) {
+  __shared__ int first_tile;
+  const int b = first_req + blockIdx.x, hd = blockIdx.y;
+  const int e = blockIdx.z * 256 + threadIdx.x;
   pdl_wait();
   pdl_launch_dependents();
   const int slot = state_slots[b];
   const int tok0 = cu_seqlens[b], n_tok = cu_seqlens[b + 1] - tok0;
   if (slot < 0 || n_tok <= 0) return;
+  if (threadIdx.x == 0) first_tile = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_tiles; i += 256)           // a request's chunks follow one another in the list
+    if (tiles[2 * i] == b && tiles[2 * i + 1] == 0) first_tile = i;
+  __syncthreads();
+  const int c0 = first_tile;
+  if (c0 < 0 || e >= D * V) return;
+  const int d = e / V;
   const bool fresh = context_lens[b] - n_tok == 0;
-  float* Sg = S_state + ((int64_t)slot * H + hd) * D * V;
-  for (int d = dy; d < D; d += GLA_DY) S[d * (VB + 1) + vc] = (fresh || !v_ok) ? 0.f : Sg[(int64_t)d * V + v0 + vc];
-
-  for (int t0 = 0; t0 < n_tok; t0 += LC) {
-    const int L = min(LC, n_tok - t0);
-    __syncthreads();                            // the chunk before is done with everything
-    for (int d = tid; d < D; d += GLA_THREADS) bL[d] = bsum[(int64_t)(tok0 + t0 + L - 1) * H * D + hd * D + d];
-    __syncthreads();
-    for (int idx = tid; idx < LC * D; idx += GLA_THREADS) {
-      const int t = idx / D, d = idx - t * D;
-      float qv = 0.f, kv = 0.f;
-      if (t < L) {
-        const float* row = proj + (int64_t)(tok0 + t0 + t) * ld;
-        const float bt = bsum[(int64_t)(tok0 + t0 + t) * H * D + hd * D + d];
-        qv = row[off_q + hd * D + d] * q_scale * exp2f(bt);
-        kv = row[off_k + hd * D + d] * exp2f(bL[d] - bt);
-      }
-      Qt[t * ldq + d] = qv;
-      Kt[t * ldq + d] = kv;
+  float* Sg = S_state + ((int64_t)slot * H + hd) * D * V + e;
+  float S = fresh ? 0.f : *Sg;
+  const int n_chunks = (n_tok + GLA_LC - 1) / GLA_LC;
+  const int64_t step = (int64_t)H * D * V;
+  float* st = states + ((int64_t)c0 * H + hd) * D * V + e;
+  const float* bd = bsum + (int64_t)tok0 * H * D + hd * D + d;
+  constexpr int AHEAD = 8;                      // loads in flight a thread: a chunk's loads do not wait for the chunk before
+  for (int c0 = 0; c0 < n_chunks; c0 += AHEAD) {
+    float u[AHEAD], dec[AHEAD];
+#pragma unroll
+    for (int j = 0; j < AHEAD; ++j) {
+      const int c = min(c0 + j, n_chunks - 1);
+      u[j] = st[c * step];
+      dec[j] = bd[(int64_t)(min((c + 1) * GLA_LC, n_tok) - 1) * H * D];
     }
-    for (int idx = tid; idx < LC * VB; idx += GLA_THREADS) {
-      const int t = idx / VB, v = idx - t * VB;
-      Vc[t * (VB + 1) + v] = (t < L && v0 + v < V) ? proj[(int64_t)(tok0 + t0 + t) * ld + off_v + hd * V + v0 + v] : 0.f;
-    }
-    for (int idx = tid; idx < LC * LC; idx += GLA_THREADS) {
-      const int t = idx / LC, s2 = idx - t * LC;
-      Ac[t * (LC + 1) + s2] = t < L ? A[((int64_t)(tok0 + t0 + t) * H + hd) * LC + s2] : 0.f;
-    }
-    __syncthreads();
-    for (int d = tid; d < D; d += GLA_THREADS) bL[d] = exp2f(bL[d]);      // (read as B_L above; as the decay of S below)
-    {   // o: rows t = dy + GLA_DY i of column vc
-      float num[LC / GLA_DY] = {};
-      for (int s2 = 0; s2 < L; ++s2) {
-        const float vv = Vc[s2 * (VB + 1) + vc];
 #pragma unroll
-        for (int i = 0; i < LC / GLA_DY; ++i) num[i] = fmaf(Ac[(dy + GLA_DY * i) * (LC + 1) + s2], vv, num[i]);
-      }
-      for (int d = 0; d < D; ++d) {
-        const float sv = S[d * (VB + 1) + vc];
-#pragma unroll
-        for (int i = 0; i < LC / GLA_DY; ++i) num[i] = fmaf(Qt[(dy + GLA_DY * i) * ldq + d], sv, num[i]);
-      }
-      if (v_ok) {
-#pragma unroll
-        for (int i = 0; i < LC / GLA_DY; ++i) {
-          const int t = dy + GLA_DY * i;
-          if (t < L) o[(int64_t)(tok0 + t0 + t) * H * V + hd * V + v0 + vc] = num[i];
-        }
-      }
-    }
-    __syncthreads();                            // everyone has read the old S; exp(B_L) is written
-    {   // the state behind the chunk
-      float acc[MAXD / GLA_DY] = {};
-      for (int s2 = 0; s2 < L; ++s2) {
-        const float vv = Vc[s2 * (VB + 1) + vc];
-#pragma unroll
-        for (int i = 0; i < MAXD / GLA_DY; ++i) {
-          const int d = dy + GLA_DY * i;
-          if (d < D) acc[i] = fmaf(Kt[s2 * ldq + d], vv, acc[i]);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < MAXD / GLA_DY; ++i) {
-        const int d = dy + GLA_DY * i;
-        if (d < D) S[d * (VB + 1) + vc] = fmaf(bL[d], S[d * (VB + 1) + vc], acc[i]);
+    for (int j = 0; j < AHEAD; ++j) {
+      if (c0 + j < n_chunks) {
+        st[(c0 + j) * step] = S;
+        S = fmaf(exp2f(dec[j]), S, u[j]);
       }
     }
   }
+  *Sg = S;
+}
+
+// One block = one chunk x one head x GLA_VT columns.  states[c] holds the state in front of the chunk.
+__global__ void __launch_bounds__(256)
+gla_chunk_out_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_v, const float* __restrict__ bsum,
+                     const float* __restrict__ A, const float* __restrict__ states, const int* __restrict__ cu_seqlens,
+                     const int* __restrict__ tiles, float* __restrict__ o, int H, int D, int V, float q_scale) {
+  extern __shared__ float smem[];
+  constexpr int LC = GLA_LC, VT = GLA_VT;
+  const int Kn = D + LC, ldx = Kn + 1;
+  float* X = smem;                              // [LC][D + LC + 1]   q_t * exp(B_t), then A[t][.]; zero rows beyond L
+  float* Y = X + LC * ldx;                      // [D + LC][VT]       the state, then the chunk's v; zero rows beyond L
+  const int tid = threadIdx.x, hd = blockIdx.y, v0 = blockIdx.z * VT;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int b = tiles[2 * blockIdx.x], q0 = tiles[2 * blockIdx.x + 1];
+  const int tok0 = cu_seqlens[b] + q0;
+  const int L = min(LC, cu_seqlens[b + 1] - tok0);
+  if (L <= 0) return;
+  // the fills load from clamped places and select afterwards, so that the loads of several turns are in flight together
+#pragma unroll 8
+  for (int idx = tid; idx < LC * D; idx += 256) {
+    const int t = idx / D, c = idx - t * D;
+    const int tc = min(t, L - 1);
+    const float x = proj[(int64_t)(tok0 + tc) * ld + off_q + hd * D + c] * q_scale *
+                    exp2f(bsum[(int64_t)(tok0 + tc) * H * D + hd * D + c]);
+    X[t * ldx + c] = t < L ? x : 0.f;
+  }
+#pragma unroll 8
+  for (int idx = tid; idx < LC * LC; idx += 256) {
+    const int t = idx / LC, c = idx - t * LC;
+    const float x = A[((int64_t)(tok0 + min(t, L - 1)) * H + hd) * LC + c];
+    X[t * ldx + D + c] = t < L ? x : 0.f;
+  }
+  const float* st = states + ((int64_t)blockIdx.x * H + hd) * D * V;
+#pragma unroll 8
+  for (int idx = tid; idx < D * VT; idx += 256) {
+    const int r = idx / VT, v = idx - r * VT;
+    const float y = st[(int64_t)r * V + min(v0 + v, V - 1)];
+    Y[idx] = v0 + v < V ? y : 0.f;
+  }
+#pragma unroll 8
+  for (int idx = tid; idx < LC * VT; idx += 256) {
+    const int r = idx / VT, v = idx - r * VT;
+    const float y = proj[(int64_t)(tok0 + min(r, L - 1)) * ld + off_v + hd * V + min(v0 + v, V - 1)];
+    Y[D * VT + idx] = (r < L && v0 + v < V) ? y : 0.f;
+  }
   __syncthreads();
-  if (v_ok)
-    for (int d = dy; d < D; d += GLA_DY) Sg[(int64_t)d * V + v0 + vc] = S[d * (VB + 1) + vc];
+  const int ty = tid / 16, tx = tid % 16;
+  float acc[4][4] = {};
+  for (int c = 0; c < Kn; ++c) {
+    float xx[4], yy[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) xx[i] = X[(ty + 16 * i) * ldx + c];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) yy[j] = Y[c * VT + tx + 16 * j];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xx[i], yy[j], acc[i][j]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int t = ty + 16 * i;
+    if (t >= L) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int v = v0 + tx + 16 * j;
+      if (v < V) o[(int64_t)(tok0 + t) * H * V + hd * V + v] = acc[i][j];
+    }
+  }
 }
 
 // proj: [T, ld] float32 rows; the low-rank vector sits at columns [off_a1, off_a1 + rank).  w2: [C, rank] of w_dtype,
@@ -279,9 +384,11 @@ gla_chunk_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_
 ME_API int me_gla_decay(const float* proj, int64_t ld, int off_a1, int rank, const void* w2, int w_dtype, const float* bias,
                         float tau, float* la, int T, int C, cudaStream_t stream) {
   if (T == 0) return 0;
-  ME_REQUIRE(T > 0 && C > 0 && rank > 0 && rank <= 8192 && tau > 0.f, "me_gla_decay: bad sizes T=%d C=%d rank=%d tau=%g", T, C, rank, tau);
-  ME_DISPATCH_DTYPE(w_dtype, TW, me_launch(gla_decay_kernel<TW>, dim3(T, (C + 255) / 256), dim3(256), sizeof(float) * rank, stream, proj,
-                                           ld, off_a1, rank, (const TW*)w2, bias, 1.0f / tau, la, C));
+  ME_REQUIRE(T > 0 && C > 0 && rank > 0 && rank <= 1024 && tau > 0.f, "me_gla_decay: bad sizes T=%d C=%d rank=%d tau=%g", T, C, rank, tau);
+  ME_REQUIRE((C + 127) / 128 <= 65535, "me_gla_decay: too many channels (%d)", C);
+  ME_DISPATCH_DTYPE(w_dtype, TW, me_launch(gla_decay_kernel<TW>, dim3((T + GLA_DT - 1) / GLA_DT, (C + 127) / 128), dim3(128),
+                                           sizeof(float) * GLA_DT * rank, stream, proj, ld, off_a1, rank, (const TW*)w2, bias,
+                                           1.0f / tau, la, T, C));
   ME_LAUNCH_CHECK("me_gla_decay");
   return 0;
 }
@@ -289,7 +396,8 @@ ME_API int me_gla_decay(const float* proj, int64_t ld, int off_a1, int rank, con
 // proj: [T, ld] float32 rows holding q, k (H*D each) and v (H*V) at the given column offsets; la: [T, H*D] float32 log decays
 // (overwritten with the chunks' sums where the chunk kernels run).  S_state [slots, H, D, V] float32.  o: [T, H*V] float32.
 // Requests [0, num_decodes) are walked token by token.  The others too, unless ``tiles`` ([n_tiles, 2] int32: request and
-// first token of every run of GLA_LC tokens of the requests from num_decodes on) and ``A_ws`` ([T, H, GLA_LC] float32) are given.
+// first token of every run of GLA_LC tokens of the requests from num_decodes on, a request's runs in order and side by side),
+// ``A_ws`` ([T, H, GLA_LC] float32) and ``states_ws`` ([n_tiles, H, D, V] float32) are given.
 template <typename K>
 static int gla_raise_smem(K kernel, size_t smem, const char* what) {
   if (smem > 48 * 1024) {
@@ -303,21 +411,24 @@ ME_API int me_gla_chunk_len() { return GLA_LC; }
 
 ME_API int me_gla_scan(const float* proj, int64_t ld, int off_q, int off_k, int off_v, float* la, float* S_state,
                        const int* cu_seqlens, const int* context_lens, const int* state_slots, float* o, int B, int H, int D, int V,
-                       float q_scale, const int* tiles, int n_tiles, int num_decodes, float* A_ws, cudaStream_t stream) {
+                       float q_scale, const int* tiles, int n_tiles, int num_decodes, float* A_ws, float* states_ws,
+                       cudaStream_t stream) {
   if (B == 0) return 0;
   ME_REQUIRE(B > 0 && H > 0 && D > 0 && V > 0, "me_gla_scan: bad sizes B=%d H=%d D=%d V=%d", B, H, D, V);
   ME_REQUIRE(H <= 65535 && num_decodes >= 0 && num_decodes <= B, "me_gla_scan: too many heads, or %d single-token requests of %d", num_decodes, B);
-  const dim3 vblocks(1, H, (V + GLA_VB - 1) / GLA_VB);
+  const int Dp = (D + 63) / 64 * 64, v_tiles = (V + GLA_VT - 1) / GLA_VT;
   const size_t smem_intra = sizeof(float) * 3 * GLA_LC * ((size_t)D + 1);
-  const size_t smem_chunk = sizeof(float) * ((size_t)D * (GLA_VB + 1) + 2 * GLA_LC * ((size_t)D + 1) + GLA_LC * (GLA_VB + 1) +
-                                             GLA_LC * (GLA_LC + 1) + (size_t)D);
-  const bool chunks = tiles && A_ws && n_tiles > 0 && num_decodes < B && D <= 256 && smem_intra <= 220 * 1024 && smem_chunk <= 220 * 1024;
+  const size_t smem_state = sizeof(float) * (GLA_LC * ((size_t)Dp + 1) + GLA_LC * GLA_VT);
+  const size_t smem_out = sizeof(float) * (GLA_LC * ((size_t)D + GLA_LC + 1) + ((size_t)D + GLA_LC) * GLA_VT);
+  const bool chunks = tiles && A_ws && states_ws && n_tiles > 0 && num_decodes < B && D <= 256 && v_tiles <= 65535 &&
+                      ((int64_t)D * V + 255) / 256 <= 65535 && smem_intra <= 220 * 1024 && smem_state <= 220 * 1024 &&
+                      smem_out <= 220 * 1024;
   const int n_scan = chunks ? num_decodes : B;
   if (n_scan > 0) {
     const size_t smem = sizeof(float) * ((size_t)D * (GLA_VB + 1) + 3 * (size_t)D + GLA_DY * GLA_VB);
     ME_REQUIRE(smem <= 200 * 1024, "me_gla_scan: head size %d is too large", D);
     if (gla_raise_smem(gla_scan_kernel, smem, "me_gla_scan")) return 1;
-    me_launch(gla_scan_kernel, dim3(n_scan, vblocks.y, vblocks.z), dim3(GLA_THREADS), smem, stream, proj, ld, off_q, off_k, off_v,
+    me_launch(gla_scan_kernel, dim3(n_scan, H, (V + GLA_VB - 1) / GLA_VB), dim3(GLA_THREADS), smem, stream, proj, ld, off_q, off_k, off_v,
               (const float*)la, S_state, cu_seqlens, context_lens, state_slots, o, H, D, V, q_scale);
     ME_LAUNCH_CHECK("me_gla_scan");
   }
@@ -326,18 +437,17 @@ ME_API int me_gla_scan(const float* proj, int64_t ld, int off_q, int off_k, int 
     me_launch(gla_intra_kernel, dim3(n_tiles, H), dim3(256), smem_intra, stream, proj, ld, off_q, off_k, la, cu_seqlens, tiles, A_ws, H,
               D, q_scale);
     ME_LAUNCH_CHECK("me_gla_scan (intra)");
-    const dim3 grid(B - num_decodes, vblocks.y, vblocks.z);
-#define GLA_CHUNK(MAXD)                                                                                                         \
-  do {                                                                                                                          \
-    if (gla_raise_smem(gla_chunk_kernel<MAXD>, smem_chunk, "me_gla_scan (chunks)")) return 1;                                   \
-    me_launch(gla_chunk_kernel<MAXD>, grid, dim3(GLA_THREADS), smem_chunk, stream, proj, ld, off_q, off_k, off_v, (const float*)la, \
-              (const float*)A_ws, S_state, cu_seqlens, context_lens, state_slots, o, num_decodes, H, D, V, q_scale);           \
-  } while (0)
-    if (D <= 64) GLA_CHUNK(64);
-    else if (D <= 128) GLA_CHUNK(128);
-    else GLA_CHUNK(256);
-#undef GLA_CHUNK
-    ME_LAUNCH_CHECK("me_gla_scan (chunks)");
+    if (gla_raise_smem(gla_chunk_state_kernel, smem_state, "me_gla_scan (chunk states)")) return 1;
+    me_launch(gla_chunk_state_kernel, dim3(n_tiles, H, v_tiles), dim3(256), smem_state, stream, proj, ld, off_k, off_v, (const float*)la,
+              cu_seqlens, tiles, states_ws, H, D, V);
+    ME_LAUNCH_CHECK("me_gla_scan (chunk states)");
+    me_launch(gla_state_walk_kernel, dim3(B - num_decodes, H, (int)(((int64_t)D * V + 255) / 256)), dim3(256), 0, stream,
+              (const float*)la, states_ws, S_state, cu_seqlens, context_lens, state_slots, tiles, n_tiles, num_decodes, H, D, V);
+    ME_LAUNCH_CHECK("me_gla_scan (state walk)");
+    if (gla_raise_smem(gla_chunk_out_kernel, smem_out, "me_gla_scan (chunk outputs)")) return 1;
+    me_launch(gla_chunk_out_kernel, dim3(n_tiles, H, v_tiles), dim3(256), smem_out, stream, proj, ld, off_q, off_v, (const float*)la,
+              (const float*)A_ws, (const float*)states_ws, cu_seqlens, tiles, o, H, D, V, q_scale);
+    ME_LAUNCH_CHECK("me_gla_scan (chunk outputs)");
   }
   return 0;
 }

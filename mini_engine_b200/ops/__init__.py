@@ -60,7 +60,7 @@ _PROTOS = {
     "me_parallel_norm": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
     "me_attn_prep": [_P, _L, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_gla_decay": [_P, _L, _I, _I, _P, _I, _P, _F, _P, _I, _I, _P],
-    "me_gla_scan": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P],
+    "me_gla_scan": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P, _P],
     "me_activation": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _P],
     "me_soft_cap": [_P, _L, _F, _P],
     "me_add_row_vector": [_P, _I, _I, _I, _P, _P],
@@ -1150,25 +1150,37 @@ GLA_CHUNK = 64        # tokens that the chunk kernels of csrc/gla.cu take at a t
 
 
 def gla_scan(proj: torch.Tensor, offsets: dict, la: torch.Tensor, S: torch.Tensor, meta, state_slots: torch.Tensor, o: torch.Tensor,
-             num_heads: int, dim: int, vdim: int, q_scale: float, scores: Optional[torch.Tensor] = None) -> None:
+             num_heads: int, dim: int, vdim: int, q_scale: float, scores: Optional[torch.Tensor] = None,
+             chunk_states: Optional[torch.Tensor] = None) -> None:
     """Walks every request's tokens of this step through S_t = diag(exp(la_t)) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t from the
     state in its slot (see csrc/gla.cu).  ``proj`` [T, N] float32 holds q, k, v at the column ``offsets``; ``la`` [T, heads * dim]
-    and ``o`` [T, heads * vdim] float32.  With ``scores`` ([T, heads, GLA_CHUNK] float32 workspace) the requests that bring
-    several tokens take GLA_CHUNK tokens at a time (``gla_chunks``); ``la`` is overwritten on the way."""
+    and ``o`` [T, heads * vdim] float32.  With the float32 workspaces ``scores`` ([T, heads, GLA_CHUNK]) and ``chunk_states``
+    (heads * dim * vdim values for every run of GLA_CHUNK tokens: ``gla_chunk_count``) the requests that bring several tokens
+    take GLA_CHUNK tokens at a time, all runs of the step side by side (``gla_chunks``); ``la`` is overwritten on the way."""
     T = proj.shape[0]
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1, "gla_scan: projections must be float32 rows")
     _need(all(t.dtype == torch.float32 and t.is_contiguous() for t in (S, la, o)), "gla_scan: float32 state, decays and output")
     _need(tuple(S.shape[1:]) == (num_heads, dim, vdim) and tuple(la.shape) == (T, num_heads * dim)
           and tuple(o.shape) == (T, num_heads * vdim), "gla_scan: shapes")
     tiles, n_tiles = meta.tile_lists[GLA_CHUNK]
-    chunked = gla_chunks and scores is not None and n_tiles > 0
+    chunked = gla_chunks and scores is not None and chunk_states is not None and n_tiles > 0
     if chunked:
         _need(scores.dtype == torch.float32 and scores.is_contiguous() and scores.numel() >= T * num_heads * GLA_CHUNK,
               "gla_scan: the workspace of scores is float32 [T, heads, GLA_CHUNK]")
+        _need(chunk_states.dtype == torch.float32 and chunk_states.is_contiguous()
+              and chunk_states.numel() >= n_tiles * num_heads * dim * vdim,
+              "gla_scan: the workspace of states is float32 [runs of GLA_CHUNK tokens, heads, dim, vdim]")
     _call("me_gla_scan", proj.data_ptr(), proj.stride(0), offsets["q"], offsets["k"], offsets["v"], la.data_ptr(), S.data_ptr(),
           meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), state_slots.data_ptr(), o.data_ptr(), meta.num_reqs,
           num_heads, dim, vdim, float(q_scale), tiles.data_ptr() if chunked else 0, n_tiles if chunked else 0, meta.num_decodes,
-          scores.data_ptr() if chunked else 0, _stream())
+          scores.data_ptr() if chunked else 0, chunk_states.data_ptr() if chunked else 0, _stream())
+
+
+def gla_chunk_count(meta) -> int:
+    """An upper bound of the runs of GLA_CHUNK tokens that the step's requests with several tokens are cut into (a bound that
+    depends on the step's shape only, so that a recorded step keeps its workspace)."""
+    multi = meta.num_reqs - meta.num_decodes
+    return 0 if multi <= 0 else (meta.num_tokens - meta.num_decodes) // GLA_CHUNK + multi
 
 
 # ---- attention through a latent --------------------------------------------------------------------

@@ -60,9 +60,11 @@ class GatedLinearAttention(Mixer):
         la = ctx.buffer("gla_log_decay", (T, H * D), torch.float32)
         ops.gla_decay(proj, self.offsets["a1"], self.decay_rank, self.p("a2"), self.p("a2.b"), self.tau, la)
         o = ctx.buffer("gla_o", (T, H * V), torch.float32)
-        scores = ctx.buffer("gla_scores", (T, H, ops.GLA_CHUNK), torch.float32) if T > ctx.attn_meta.num_decodes else None
+        runs = ops.gla_chunk_count(ctx.attn_meta)
+        scores = ctx.buffer("gla_scores", (T, H, ops.GLA_CHUNK), torch.float32) if runs else None
+        chunk_states = ctx.buffer("gla_chunk_states", (runs, H, D, V), torch.float32) if runs else None
         ops.gla_scan(proj, self.offsets, la, ctx.state(call.cache_slot, "S"), ctx.attn_meta, ctx.state_slots, o, H, D, V, D ** -0.5,
-                     scores=scores)
+                     scores=scores, chunk_states=chunk_states)
         gated = ctx.buffer("gla_gated", (T, H * V), ctx.act_dtype)
         ops.mlstm_out(o, proj, self.offsets["g"], self.p("norm"), self.norm_eps, gated, H, V, shared_weight=True, gate="silu")
         return self.o_proj.forward(gated, ctx, "mixer_out")
