@@ -28,7 +28,7 @@ def _meta(lens, contexts):
     assert all(n == 1 for n in lens[:D]) and all(n > 1 for n in lens[D:])
     cu = np.concatenate(([0], np.cumsum(lens))).astype(np.int32)
     lists = {}
-    for tq in (8, 16, 32, 64):
+    for tq in _ops().ATTN_TILE_SIZES:
         tiles = [(b, q0) for b in range(D, len(lens)) for q0 in range(0, lens[b], tq)]
         lists[tq] = (torch.tensor(tiles or [(0, 0)], dtype=torch.int32, device=DEV), len(tiles))
     return SimpleNamespace(cu_seqlens=torch.tensor(cu, device=DEV), context_lens=torch.tensor(contexts, dtype=torch.int32, device=DEV),
@@ -65,12 +65,12 @@ class _GlaRunner:
             self.offs[k], o = o, o + w[k].shape[0]
         self.S = torch.full((slots, H, D, V), float("nan"), device=DEV)
 
-    def step(self, rows, lens, contexts, slots):
+    def step(self, rows, lens, contexts, slots, proj=None):
         """rows: the step's inputs [sum(lens), W] in the order of the requests (single tokens first)."""
         ops, m, w = self.ops, self.m, self.w
         H, D, V = m["heads"], m["dim"], m["vdim"]
         T = rows.shape[0]
-        proj = (rows.to(DEV) @ self.packed.T).contiguous()
+        proj = (rows.to(DEV) @ self.packed.T).contiguous() if proj is None else proj
         meta = _meta(list(lens), list(contexts))
         la = torch.empty(T, H * D, device=DEV)
         ops.gla_decay(proj, self.offs["a1"], w["a1"].shape[0], w["a2"].to(DEV), w["a2.b"].to(DEV), m["tau"], la)
@@ -87,8 +87,9 @@ class _GlaRunner:
 
     def sequence(self, h, cuts, slot):
         outs, pos = [], 0
+        all_proj = h.to(DEV) @ self.packed.T             # once for the whole sequence: a product's rounding may depend on its rows
         for c in cuts:
-            outs.append(self.step(h[pos:pos + c], [c], [pos + c], [slot]))
+            outs.append(self.step(h[pos:pos + c], [c], [pos + c], [slot], proj=all_proj[pos:pos + c].contiguous()))
             pos += c
         return torch.cat(outs)
 
