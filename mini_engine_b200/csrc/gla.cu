@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(GLA_THREADS)
 gla_scan_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_k, int off_v, const float* __restrict__ la,
                 float* __restrict__ S_state, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                 const int* __restrict__ state_slots, float* __restrict__ o, int H, int D, int V, float q_scale) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   float* S = smem;                              // [D][GLA_VB + 1]
   float* q_s = S + D * (GLA_VB + 1);            // [D]
   float* k_s = q_s + D;                         // [D]
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(256)
 gla_intra_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_k, float* __restrict__ la,
                  const int* __restrict__ cu_seqlens, const int* __restrict__ tiles, float* __restrict__ A, int H, int D,
                  float q_scale) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   constexpr int LC = GLA_LC;
   const int ldq = D + 1;
   float* Qc = smem;                             // [LC][D + 1]
@@ -193,8 +193,8 @@ gla_intra_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_
 //   gla_state_walk_kernel    per request, in order: states[c] <- the state in front of chunk c; S <- diag(exp(B_L)) S + U_c;
 //                            the last S goes to the request's slot
 //   gla_chunk_out_kernel     o_t = [q_t * exp(B_t) | A[t][.]] [states[c]; v] of every chunk: one product over D + GLA_LC terms
-// states: [n_tiles, H, D, V] float32.  The first two kernels and the third take GLA_VT columns of S a block, 4 x 4 results a
-// thread.
+// states: [n_tiles, H, D, V] float32.  The first and the third kernel take GLA_VT columns of S a block and 4 x 4 results a
+// thread, with 16-byte loads of both operands from shared memory.
 constexpr int GLA_VT = 64;
 
 // One block = one chunk x one head x GLA_VT columns.  bsum: gla_intra_kernel's inclusive sums (units of log 2).
@@ -202,10 +202,10 @@ __global__ void __launch_bounds__(256)
 gla_chunk_state_kernel(const float* __restrict__ proj, int64_t ld, int off_k, int off_v, const float* __restrict__ bsum,
                        const int* __restrict__ cu_seqlens, const int* __restrict__ tiles, float* __restrict__ states, int H, int D,
                        int V) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   constexpr int LC = GLA_LC, VT = GLA_VT;
-  const int Dp = (D + 63) / 64 * 64, ldk = Dp + 1;
-  float* Kt = smem;                             // [LC][Dp + 1]   k_s * exp(B_L - B_s); zero beyond L and D
+  const int Dp = (D + 63) / 64 * 64, ldk = Dp + 4;
+  float* Kt = smem;                             // [LC][Dp + 4]   k_s * exp(B_L - B_s); zero beyond L and D
   float* Vc = Kt + LC * ldk;                    // [LC][VT]
   const int tid = threadIdx.x, hd = blockIdx.y, v0 = blockIdx.z * VT;
   pdl_wait();
@@ -231,16 +231,15 @@ gla_chunk_state_kernel(const float* __restrict__ proj, int64_t ld, int off_k, in
     Vc[idx] = (t < L && v0 + v < V) ? x : 0.f;
   }
   __syncthreads();
+  // a thread: rows d0 + 4 ty .. + 3 and columns 4 tx .. + 3; one 16-byte load of each operand a token
   const int ty = tid / 16, tx = tid % 16;
   float* out = states + ((int64_t)blockIdx.x * H + hd) * D * V;
   for (int d0 = 0; d0 < D; d0 += 64) {
     float acc[4][4] = {};
     for (int s = 0; s < L; ++s) {
-      float kk[4], vv[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) kk[i] = Kt[s * ldk + d0 + ty + 16 * i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) vv[j] = Vc[s * VT + tx + 16 * j];
+      const float4 k4 = *reinterpret_cast<const float4*>(Kt + s * ldk + d0 + 4 * ty);
+      const float4 v4 = *reinterpret_cast<const float4*>(Vc + s * VT + 4 * tx);
+      const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -248,11 +247,11 @@ gla_chunk_state_kernel(const float* __restrict__ proj, int64_t ld, int off_k, in
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const int d = d0 + ty + 16 * i;
+      const int d = d0 + 4 * ty + i;
       if (d >= D) continue;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int v = v0 + tx + 16 * j;
+        const int v = v0 + 4 * tx + j;
         if (v < V) out[(int64_t)d * V + v] = acc[i][j];
       }
     }
@@ -313,11 +312,11 @@ __global__ void __launch_bounds__(256)
 gla_chunk_out_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int off_v, const float* __restrict__ bsum,
                      const float* __restrict__ A, const float* __restrict__ states, const int* __restrict__ cu_seqlens,
                      const int* __restrict__ tiles, float* __restrict__ o, int H, int D, int V, float q_scale) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   constexpr int LC = GLA_LC, VT = GLA_VT;
-  const int Kn = D + LC, ldx = Kn + 1;
-  float* X = smem;                              // [LC][D + LC + 1]   q_t * exp(B_t), then A[t][.]; zero rows beyond L
-  float* Y = X + LC * ldx;                      // [D + LC][VT]       the state, then the chunk's v; zero rows beyond L
+  const int Dq = (D + 3) / 4 * 4, Kn = Dq + LC, ldx = Kn + 4;
+  float* X = smem;                              // [LC][Dq + LC + 4]  q_t * exp(B_t), then A[t][.]; zero rows beyond L
+  float* Y = X + LC * ldx;                      // [Dq + LC][VT]      the state, then the chunk's v; zero rows beyond D and L
   const int tid = threadIdx.x, hd = blockIdx.y, v0 = blockIdx.z * VT;
   pdl_wait();
   pdl_launch_dependents();
@@ -327,45 +326,54 @@ gla_chunk_out_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int 
   if (L <= 0) return;
   // the fills load from clamped places and select afterwards, so that the loads of several turns are in flight together
 #pragma unroll 8
-  for (int idx = tid; idx < LC * D; idx += 256) {
-    const int t = idx / D, c = idx - t * D;
-    const int tc = min(t, L - 1);
-    const float x = proj[(int64_t)(tok0 + tc) * ld + off_q + hd * D + c] * q_scale *
-                    exp2f(bsum[(int64_t)(tok0 + tc) * H * D + hd * D + c]);
-    X[t * ldx + c] = t < L ? x : 0.f;
+  for (int idx = tid; idx < LC * Dq; idx += 256) {
+    const int t = idx / Dq, c = idx - t * Dq;
+    const int tc = min(t, L - 1), cc = min(c, D - 1);
+    const float x = proj[(int64_t)(tok0 + tc) * ld + off_q + hd * D + cc] * q_scale *
+                    exp2f(bsum[(int64_t)(tok0 + tc) * H * D + hd * D + cc]);
+    X[t * ldx + c] = (t < L && c < D) ? x : 0.f;
   }
 #pragma unroll 8
   for (int idx = tid; idx < LC * LC; idx += 256) {
     const int t = idx / LC, c = idx - t * LC;
     const float x = A[((int64_t)(tok0 + min(t, L - 1)) * H + hd) * LC + c];
-    X[t * ldx + D + c] = t < L ? x : 0.f;
+    X[t * ldx + Dq + c] = t < L ? x : 0.f;
   }
   const float* st = states + ((int64_t)blockIdx.x * H + hd) * D * V;
 #pragma unroll 8
-  for (int idx = tid; idx < D * VT; idx += 256) {
+  for (int idx = tid; idx < Dq * VT; idx += 256) {
     const int r = idx / VT, v = idx - r * VT;
-    const float y = st[(int64_t)r * V + min(v0 + v, V - 1)];
-    Y[idx] = v0 + v < V ? y : 0.f;
+    const float y = st[(int64_t)min(r, D - 1) * V + min(v0 + v, V - 1)];
+    Y[idx] = (r < D && v0 + v < V) ? y : 0.f;
   }
 #pragma unroll 8
   for (int idx = tid; idx < LC * VT; idx += 256) {
     const int r = idx / VT, v = idx - r * VT;
     const float y = proj[(int64_t)(tok0 + min(r, L - 1)) * ld + off_v + hd * V + min(v0 + v, V - 1)];
-    Y[D * VT + idx] = (r < L && v0 + v < V) ? y : 0.f;
+    Y[Dq * VT + idx] = (r < L && v0 + v < V) ? y : 0.f;
   }
   __syncthreads();
+  // a thread: rows ty + 16 i and columns 4 tx .. + 3; four terms a turn with 16-byte loads of both operands
   const int ty = tid / 16, tx = tid % 16;
   float acc[4][4] = {};
-  for (int c = 0; c < Kn; ++c) {
-    float xx[4], yy[4];
+  for (int c = 0; c < Kn; c += 4) {
+    float xx[4][4], yy[4][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) xx[i] = X[(ty + 16 * i) * ldx + c];
+    for (int i = 0; i < 4; ++i) {
+      const float4 x4 = *reinterpret_cast<const float4*>(X + (ty + 16 * i) * ldx + c);
+      xx[i][0] = x4.x; xx[i][1] = x4.y; xx[i][2] = x4.z; xx[i][3] = x4.w;
+    }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) yy[j] = Y[c * VT + tx + 16 * j];
+    for (int k = 0; k < 4; ++k) {
+      const float4 y4 = *reinterpret_cast<const float4*>(Y + (c + k) * VT + 4 * tx);
+      yy[k][0] = y4.x; yy[k][1] = y4.y; yy[k][2] = y4.z; yy[k][3] = y4.w;
+    }
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int k = 0; k < 4; ++k)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xx[i], yy[j], acc[i][j]);
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(xx[i][k], yy[k][j], acc[i][j]);
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -373,7 +381,7 @@ gla_chunk_out_kernel(const float* __restrict__ proj, int64_t ld, int off_q, int 
     if (t >= L) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int v = v0 + tx + 16 * j;
+      const int v = v0 + 4 * tx + j;
       if (v < V) o[(int64_t)(tok0 + t) * H * V + hd * V + v] = acc[i][j];
     }
   }
@@ -418,8 +426,9 @@ ME_API int me_gla_scan(const float* proj, int64_t ld, int off_q, int off_k, int 
   ME_REQUIRE(H <= 65535 && num_decodes >= 0 && num_decodes <= B, "me_gla_scan: too many heads, or %d single-token requests of %d", num_decodes, B);
   const int Dp = (D + 63) / 64 * 64, v_tiles = (V + GLA_VT - 1) / GLA_VT;
   const size_t smem_intra = sizeof(float) * 3 * GLA_LC * ((size_t)D + 1);
-  const size_t smem_state = sizeof(float) * (GLA_LC * ((size_t)Dp + 1) + GLA_LC * GLA_VT);
-  const size_t smem_out = sizeof(float) * (GLA_LC * ((size_t)D + GLA_LC + 1) + ((size_t)D + GLA_LC) * GLA_VT);
+  const int Dq = (D + 3) / 4 * 4;
+  const size_t smem_state = sizeof(float) * (GLA_LC * ((size_t)Dp + 4) + GLA_LC * GLA_VT);
+  const size_t smem_out = sizeof(float) * (GLA_LC * ((size_t)Dq + GLA_LC + 4) + ((size_t)Dq + GLA_LC) * GLA_VT);
   const bool chunks = tiles && A_ws && states_ws && n_tiles > 0 && num_decodes < B && D <= 256 && v_tiles <= 65535 &&
                       ((int64_t)D * V + 255) / 256 <= 65535 && smem_intra <= 220 * 1024 && smem_state <= 220 * 1024 &&
                       smem_out <= 220 * 1024;

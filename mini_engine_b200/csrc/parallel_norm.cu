@@ -12,7 +12,29 @@
 // logits are wanted).
 #include "common.cuh"
 
-template <typename TY, typename TO>
+// Four neighbouring values at once (rows whose length is a multiple of four start on 16 bytes).
+__device__ __forceinline__ void pn_load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void pn_load4(const bf16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x), b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+}
+__device__ __forceinline__ void pn_store4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void pn_store4(bf16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<const unsigned*>(&a);
+  t.y = *reinterpret_cast<const unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+// VEC = 4: W is a multiple of four and every pointer is 16-byte aligned (8 for bfloat16); a thread takes four neighbours a
+// turn, so all loads of a row are in flight at once.  VEC = 1: any W.  The sums of a row are taken in the same order by every
+// launch of one VEC, and the host chooses VEC from W and the pointers alone.
+template <typename TY, typename TO, int VEC>
 __global__ void __launch_bounds__(256)
 parallel_norm_kernel(float* __restrict__ x, const TY* __restrict__ ya, const TY* __restrict__ yb, const float* __restrict__ va,
                      const float* __restrict__ vb, const float* __restrict__ w1, const float* __restrict__ b1,
@@ -26,30 +48,65 @@ parallel_norm_kernel(float* __restrict__ x, const TY* __restrict__ ya, const TY*
   float* xr = x + (int64_t)r * W;
   const bool changed = ya || yb || va || vb;
   float s = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    float v = xr[i];
-    if (ya) v += to_f<TY>(ya[(int64_t)r * W + i]);
-    if (yb) v += to_f<TY>(yb[(int64_t)r * W + i]);
-    if (va) v += va[i];
-    if (vb) v += vb[i];
-    if (changed && !rows) xr[i] = v;
-    row[i] = v;
-    s += v;
+  if constexpr (VEC == 4) {
+    for (int i = 4 * threadIdx.x; i < W; i += 4 * blockDim.x) {
+      float v[4], t[4];
+      pn_load4(xr + i, v);
+      if (ya) { pn_load4(ya + (int64_t)r * W + i, t); for (int j = 0; j < 4; ++j) v[j] += t[j]; }
+      if (yb) { pn_load4(yb + (int64_t)r * W + i, t); for (int j = 0; j < 4; ++j) v[j] += t[j]; }
+      if (va) { pn_load4(va + i, t); for (int j = 0; j < 4; ++j) v[j] += t[j]; }
+      if (vb) { pn_load4(vb + i, t); for (int j = 0; j < 4; ++j) v[j] += t[j]; }
+      if (changed && !rows) pn_store4(xr + i, v);
+      pn_store4(row + i, v);
+      s += (v[0] + v[1]) + (v[2] + v[3]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = xr[i];
+      if (ya) v += to_f<TY>(ya[(int64_t)r * W + i]);
+      if (yb) v += to_f<TY>(yb[(int64_t)r * W + i]);
+      if (va) v += va[i];
+      if (vb) v += vb[i];
+      if (changed && !rows) xr[i] = v;
+      row[i] = v;
+      s += v;
+    }
   }
   const float mean = block_sum(s, red) / (float)W;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {      // (a thread reads back what it wrote itself)
-    const float d = row[i] - mean;
-    ss = fmaf(d, d, ss);
+  if constexpr (VEC == 4) {
+    for (int i = 4 * threadIdx.x; i < W; i += 4 * blockDim.x) {      // (a thread reads back what it wrote itself)
+      float v[4];
+      pn_load4(row + i, v);
+      const float d0 = v[0] - mean, d1 = v[1] - mean, d2 = v[2] - mean, d3 = v[3] - mean;
+      ss += fmaf(d0, d0, d1 * d1) + fmaf(d2, d2, d3 * d3);
+    }
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const float d = row[i] - mean;
+      ss = fmaf(d, d, ss);
+    }
   }
   const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
-  if (out1) {
-    TO* o = out1 + (int64_t)blockIdx.x * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) o[i] = from_f<TO>(fmaf((row[i] - mean) * rstd, w1[i], b1 ? b1[i] : 0.f));
-  }
-  if (out2) {
-    TO* o = out2 + (int64_t)blockIdx.x * W;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) o[i] = from_f<TO>(fmaf((row[i] - mean) * rstd, w2[i], b2 ? b2[i] : 0.f));
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    TO* out = which ? out2 : out1;
+    const float* w = which ? w2 : w1;
+    const float* b = which ? b2 : b1;
+    if (!out) continue;
+    TO* o = out + (int64_t)blockIdx.x * W;
+    if constexpr (VEC == 4) {
+      for (int i = 4 * threadIdx.x; i < W; i += 4 * blockDim.x) {
+        float v[4], ww[4], bb[4] = {0.f, 0.f, 0.f, 0.f};
+        pn_load4(row + i, v);
+        pn_load4(w + i, ww);
+        if (b) pn_load4(b + i, bb);
+        for (int j = 0; j < 4; ++j) v[j] = fmaf((v[j] - mean) * rstd, ww[j], bb[j]);
+        pn_store4(o + i, v);
+      }
+    } else {
+      for (int i = threadIdx.x; i < W; i += blockDim.x) o[i] = from_f<TO>(fmaf((row[i] - mean) * rstd, w[i], b ? b[i] : 0.f));
+    }
   }
 }
 
@@ -61,18 +118,30 @@ ME_API int me_parallel_norm(float* x, const void* ya, const void* yb, int y_dtyp
   if (n == 0) return 0;
   ME_REQUIRE(n > 0 && W > 0 && W <= 24576, "me_parallel_norm: bad sizes n=%d W=%d", n, W);
   ME_REQUIRE((!out1 || w1) && (!out2 || w2), "me_parallel_norm: a norm needs its weight");
-  const int threads = W >= 2048 ? 256 : (W >= 512 ? 128 : 64);
+  auto misaligned = [](const void* p, size_t to) { return p && ((uintptr_t)p % to) != 0; };
+  const size_t y_al = y_dtype == ME_F32 ? 16 : 8, o_al = out_dtype == ME_F32 ? 16 : 8;
+  const bool vec = W % 4 == 0 && !misaligned(x, 16) && !misaligned(ya, y_al) && !misaligned(yb, y_al) && !misaligned(va, 16) &&
+                   !misaligned(vb, 16) && !misaligned(w1, 16) && !misaligned(b1, 16) && !misaligned(w2, 16) && !misaligned(b2, 16) &&
+                   !misaligned(out1, o_al) && !misaligned(out2, o_al);
+  const int per = vec ? 4 : 1;
+  const int threads = W >= 256 * per ? 256 : (W >= 128 * per ? 128 : 64);
   const size_t smem = sizeof(float) * W;
+#define PN_LAUNCH(VEC)                                                                                                          \
+  do {                                                                                                                          \
+    static bool attr_set = false;                                                                                               \
+    if (!attr_set) {                                                                                                            \
+      cudaError_t e = cudaFuncSetAttribute(parallel_norm_kernel<TY, TO, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+      ME_REQUIRE(e == cudaSuccess, "me_parallel_norm: cannot raise shared memory");                                             \
+      attr_set = true;                                                                                                          \
+    }                                                                                                                           \
+    me_launch(parallel_norm_kernel<TY, TO, VEC>, dim3(n), dim3(threads), smem, stream, x, (const TY*)ya, (const TY*)yb, va, vb, w1, b1, \
+              (TO*)out1, w2, b2, (TO*)out2, rows, W, eps);                                                                      \
+  } while (0)
   ME_DISPATCH_DTYPE((ya || yb) ? y_dtype : ME_F32, TY, ME_DISPATCH_DTYPE(out_dtype, TO, {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(parallel_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      ME_REQUIRE(e == cudaSuccess, "me_parallel_norm: cannot raise shared memory");
-      attr_set = true;
-    }
-    me_launch(parallel_norm_kernel<TY, TO>, dim3(n), dim3(threads), smem, stream, x, (const TY*)ya, (const TY*)yb, va, vb, w1, b1,
-              (TO*)out1, w2, b2, (TO*)out2, rows, W, eps);
+    if (vec) PN_LAUNCH(4);
+    else PN_LAUNCH(1);
   }));
+#undef PN_LAUNCH
   ME_LAUNCH_CHECK("me_parallel_norm");
   return 0;
 }
