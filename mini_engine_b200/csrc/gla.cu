@@ -12,6 +12,7 @@
 //                 the sequence was cut beyond the order of sums.  One block = one request x one head x GLA_VB columns of S.
 //                 Portions of prompts take GLA_LC tokens at a time (see gla_intra_kernel and the three kernels behind it).
 #include "common.cuh"
+#include <type_traits>
 
 constexpr int GLA_VB = 16, GLA_DY = 16, GLA_THREADS = GLA_VB * GLA_DY;
 
@@ -258,15 +259,17 @@ gla_chunk_state_kernel(const float* __restrict__ proj, int64_t ld, int off_k, in
   }
 }
 
-// One block = one request (first_req + blockIdx.x) x one head x 256 elements of S.  The loads of a chunk do not wait for the
-// chunk before; only the multiply-add does.
+// One block = one request (first_req + blockIdx.x) x one head x 256 * VEC elements of S; a thread walks VEC neighbours of one
+// row (VEC = 4: V is a multiple of four, 16-byte loads and stores).  The loads of a chunk do not wait for the chunk before;
+// only the multiply-add does.
+template <int VEC>
 __global__ void __launch_bounds__(256)
 gla_state_walk_kernel(const float* __restrict__ bsum, float* __restrict__ states, float* __restrict__ S_state,
                       const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens, const int* __restrict__ state_slots,
                       const int* __restrict__ tiles, int n_tiles, int first_req, int H, int D, int V) {
   __shared__ int first_tile;
   const int b = first_req + blockIdx.x, hd = blockIdx.y;
-  const int e = blockIdx.z * 256 + threadIdx.x;
+  const int e = (blockIdx.z * 256 + threadIdx.x) * VEC;
   pdl_wait();
   pdl_launch_dependents();
   const int slot = state_slots[b];
@@ -281,30 +284,35 @@ gla_state_walk_kernel(const float* __restrict__ bsum, float* __restrict__ states
   if (c0 < 0 || e >= D * V) return;
   const int d = e / V;
   const bool fresh = context_lens[b] - n_tok == 0;
-  float* Sg = S_state + ((int64_t)slot * H + hd) * D * V + e;
-  float S = fresh ? 0.f : *Sg;
+  using vec_t = typename std::conditional<VEC == 4, float4, float>::type;
+  vec_t* Sg = reinterpret_cast<vec_t*>(S_state + ((int64_t)slot * H + hd) * D * V + e);
+  __align__(16) float S[VEC] = {};
+  if (!fresh) *reinterpret_cast<vec_t*>(S) = *Sg;
   const int n_chunks = (n_tok + GLA_LC - 1) / GLA_LC;
   const int64_t step = (int64_t)H * D * V;
   float* st = states + ((int64_t)c0 * H + hd) * D * V + e;
   const float* bd = bsum + (int64_t)tok0 * H * D + hd * D + d;
-  constexpr int AHEAD = 8;                      // loads in flight a thread: a chunk's loads do not wait for the chunk before
-  for (int c0 = 0; c0 < n_chunks; c0 += AHEAD) {
-    float u[AHEAD], dec[AHEAD];
+  constexpr int AHEAD = VEC == 4 ? 4 : 8;       // chunks whose loads are in flight together
+  for (int c1 = 0; c1 < n_chunks; c1 += AHEAD) {
+    __align__(16) float u[AHEAD][VEC];
+    float dec[AHEAD];
 #pragma unroll
     for (int j = 0; j < AHEAD; ++j) {
-      const int c = min(c0 + j, n_chunks - 1);
-      u[j] = st[c * step];
+      const int c = min(c1 + j, n_chunks - 1);
+      *reinterpret_cast<vec_t*>(u[j]) = *reinterpret_cast<const vec_t*>(st + c * step);
       dec[j] = bd[(int64_t)(min((c + 1) * GLA_LC, n_tok) - 1) * H * D];
     }
 #pragma unroll
     for (int j = 0; j < AHEAD; ++j) {
-      if (c0 + j < n_chunks) {
-        st[(c0 + j) * step] = S;
-        S = fmaf(exp2f(dec[j]), S, u[j]);
+      if (c1 + j < n_chunks) {
+        *reinterpret_cast<vec_t*>(st + (c1 + j) * step) = *reinterpret_cast<const vec_t*>(S);
+        const float a = exp2f(dec[j]);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) S[k] = fmaf(a, S[k], u[j][k]);
       }
     }
   }
-  *Sg = S;
+  *Sg = *reinterpret_cast<const vec_t*>(S);
 }
 
 // One block = one chunk x one head x GLA_VT columns.  states[c] holds the state in front of the chunk.
@@ -450,8 +458,15 @@ ME_API int me_gla_scan(const float* proj, int64_t ld, int off_q, int off_k, int 
     me_launch(gla_chunk_state_kernel, dim3(n_tiles, H, v_tiles), dim3(256), smem_state, stream, proj, ld, off_k, off_v, (const float*)la,
               cu_seqlens, tiles, states_ws, H, D, V);
     ME_LAUNCH_CHECK("me_gla_scan (chunk states)");
-    me_launch(gla_state_walk_kernel, dim3(B - num_decodes, H, (int)(((int64_t)D * V + 255) / 256)), dim3(256), 0, stream,
-              (const float*)la, states_ws, S_state, cu_seqlens, context_lens, state_slots, tiles, n_tiles, num_decodes, H, D, V);
+    const bool walk4 = V % 4 == 0 && ((uintptr_t)states_ws % 16) == 0 && ((uintptr_t)S_state % 16) == 0;
+    const int per = walk4 ? 1024 : 256;
+    const dim3 walk_grid(B - num_decodes, H, (int)(((int64_t)D * V + per - 1) / per));
+    if (walk4)
+      me_launch(gla_state_walk_kernel<4>, walk_grid, dim3(256), 0, stream, (const float*)la, states_ws, S_state, cu_seqlens,
+                context_lens, state_slots, tiles, n_tiles, num_decodes, H, D, V);
+    else
+      me_launch(gla_state_walk_kernel<1>, walk_grid, dim3(256), 0, stream, (const float*)la, states_ws, S_state, cu_seqlens,
+                context_lens, state_slots, tiles, n_tiles, num_decodes, H, D, V);
     ME_LAUNCH_CHECK("me_gla_scan (state walk)");
     if (gla_raise_smem(gla_chunk_out_kernel, smem_out, "me_gla_scan (chunk outputs)")) return 1;
     me_launch(gla_chunk_out_kernel, dim3(n_tiles, H, v_tiles), dim3(256), smem_out, stream, proj, ld, off_q, off_v, (const float*)la,
