@@ -5,8 +5,8 @@ a = sigmoid(z)^(1/tau) with z = W_a2 (W_a1 h) + b (a low-rank projection); then
 
     S_t = diag(a_t) S_(t-1) + k_t v_t^T,        o_t = S_t^T q_t          (S starts at zero)
 
-Each head's o is divided by its root mean square and multiplied by a weight of ``vdim`` values that the heads share, the
-heads are concatenated, multiplied by silu(W_g h), and projected by W_o.  S is float32 and lives in the request's state
+Every head's o is brought to unit root mean square and scaled by one weight vector of ``vdim`` values (the same for all
+heads); the joined heads then pass the gate silu(W_g h) and the output product W_o.  S is float32 and lives in the request's state
 slot; decays, their logarithms and everything of the recurrence are float32 (the packed projection returns float32).
 """
 from __future__ import annotations

@@ -4,8 +4,8 @@ One expert (and the dense form): g = min(W_gate h, limit), u = clamp(W_up h, -li
 y = g * sigmoid(alpha * g) * (u + shift), output W_down y; ``limit`` None: nothing is clamped.  ``alpha`` 1 and ``shift`` 0
 is the plain SiLU-gated form silu(g) * u.
 
-``RoutedExperts``: router logits z = W_router h + b in float32; the ``top`` experts with the largest logits are chosen
-and weighted by the softmax over the chosen logits only; the output is the weighted sum of their outputs, plus a
+``RoutedExperts``: router logits z = W_router h + b in float32; a token goes to its ``top`` experts of largest
+logit, mixed by a softmax taken over those ``top`` logits alone; the output is that mix of their outputs, plus a
 ``shared`` expert (same form, sizes of its own) that runs for every token.  Routing, grouping by expert, the per-expert
 products and the weighted sum all run on the device, so a step's shape does not depend on the routing.
 """

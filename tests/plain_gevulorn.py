@@ -187,8 +187,8 @@ def gated_expert(h, w, p):
 
 
 def routed_experts(h, w, p, mlp, chosen_out=None):
-    """The ``top`` largest router logits choose the experts; their weights are the softmax over the chosen logits only;
-    a shared expert, when the layer has one, is added for every token."""
+    """Top-k routing: a token goes to the ``top`` experts of largest router logit, mixed by a softmax taken over those
+    ``top`` logits alone; plus the shared expert, if the layer has one."""
     top = mlp["router"]["top"]
     z = h @ w[p + "router"].T
     val, idx = torch.topk(z, top, dim=-1)
@@ -212,8 +212,9 @@ def feed_forward(h, w, p, mlp):
 
 # ---- the model ------------------------------------------------------------------------------------
 def layer_runs(cfg):
-    """The order in which layers run: (layer, pass) pairs; layers start .. stop-1 run ``times`` times in a row.  ``pass``
-    is the number of the pass for the first layer of a pass (the step vector is added there), else None."""
+    """The order in which layers run, as (layer, pass) pairs: the block of layers [start, stop) is repeated ``times`` times
+    back to back.  ``pass`` numbers the repetition at its first layer (where that repetition's vector joins the stream) and is
+    None everywhere else."""
     n = len(cfg["layers"])
     loop = cfg.get("loop")
     if not loop or loop["stop"] <= loop["start"]:
