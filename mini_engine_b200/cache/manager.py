@@ -35,6 +35,7 @@ class GroupSpec:
     planes: int = 2                  # 2: keys and values; 1: one row per token and head
     keep_first: int = 0              # a window group also keeps the pages that hold the sequence's first tokens
     chunk: Optional[int] = None      # instead of a window: only the chunk that is being filled is kept (chunks from position 0)
+    every: int = 1                   # > 1: one row for every ``every`` tokens (summaries of blocks of tokens), all of them kept
 
     @property
     def keeps_all(self) -> bool:
@@ -97,7 +98,7 @@ class CacheManager:
         self.pools = [PagePool(n) for n in num_pages]
         self.state_slots = StateSlotPool(num_state_slots)
         self.prefix_caching = bool(enable_prefix_caching and not has_state and self.groups
-                                   and all(g.keeps_all for g in self.groups))
+                                   and all(g.keeps_all and g.every == 1 for g in self.groups))
         self.num_prefix_hit_tokens = 0          # tokens that requests found in the cache instead of computing them
 
     # ---- sizes -----------------------------------------------------------------------
@@ -105,8 +106,10 @@ class CacheManager:
     def num_free_pages(self) -> list[int]:
         return [p.num_free for p in self.pools]
 
-    def pages_for(self, num_tokens: int) -> int:
-        return (num_tokens + self.page_size - 1) // self.page_size
+    def pages_for(self, num_tokens: int, every: int = 1) -> int:
+        """Pages that hold the rows of this many tokens (one row a token, or one for every ``every`` tokens)."""
+        rows = (num_tokens + every - 1) // every
+        return (rows + self.page_size - 1) // self.page_size
 
     def fits_at_all(self, num_tokens: int, max_portion: Optional[int] = None) -> bool:
         """Could a request of this many tokens ever be held (with an empty pool)?
@@ -117,7 +120,7 @@ class CacheManager:
         portion = num_tokens if max_portion is None else min(num_tokens, max_portion)
         for g, pool in zip(self.groups, self.pools):
             if g.keeps_all:
-                n = need
+                n = self.pages_for(num_tokens, g.every)
             elif g.chunk is not None:
                 n = min(need, self.pages_for(g.chunk + portion) + 1)
             else:
@@ -166,10 +169,10 @@ class CacheManager:
         if n_hit and any(holder.block_tables[g] for g in range(len(self.groups))):
             raise ValueError("prefix hits can only be given to a request that holds no pages")
         computed = holder.num_computed_tokens + n_hit * ps
-        total = (computed + num_new_tokens + ps - 1) // ps
         fresh_needed = []
         for g, pool in enumerate(self.pools):
             have = len(holder.block_tables[g])
+            total = self.pages_for(computed + num_new_tokens, self.groups[g].every)
             fresh = max(0, total - have - n_hit)
             free_hits = sum(1 for p in (hits[g] if n_hit else []) if pool.ref_count[p] == 0)
             if fresh + free_hits > pool.num_free:

@@ -543,3 +543,114 @@ class GevulornConfig(ModelConfig):
         if self.loop:
             d["loop"] = self.loop
         return d
+
+
+@dataclass
+class GalupelConfig(ModelConfig):
+    """Galupel: a decoder whose sub-layers read the residual stream itself and join it through a norm of their OUTPUT,
+    x <- x + norm1(mixer(x)), x <- x + norm2(ff(x)), with RMS norms taken over ``norm.groups`` equal parts of a row; the
+    embedding passes through such a norm too, is also the output matrix, and the logits are scaled and capped.  config.json
+    keys: ``vocab``, ``width``, ``norm`` {eps, groups}, ``logit_scale`` (absent: 1), ``logit_softcap`` (absent: none) and
+    ``layers``: a list of ``{"type", "mixer", "mlp"}`` with
+
+    * type ``attention``: mixer {heads, kv_heads, dim, vdim, scale, mask {size, pool}, kv_from}: grouped-query attention
+      without positions over a window and pooled blocks of ``pool`` tokens behind it (``pool`` absent: the window alone);
+      ``kv_from`` names an earlier layer of this type whose keys and values the layer reads with its own mask;
+    * type ``latent_attention``: mixer {heads, dim, rot_dim, vdim, kv_rank, scale, rot {base, dims}, mask {size}}: attention
+      through a latent with a rotated part and a window (``rot`` and ``mask`` may be absent);
+    * mlp: null or moe {router {experts, top, groups {count, keep}}, expert {ff}} (``groups`` absent: one group).
+
+    The design has no limit on positions; ``max_position_embeddings`` is what an int32 position allows the engine."""
+
+    norm_eps: float = 0.0
+    norm_groups: int = 1
+    logit_scale: float = 1.0
+    logit_softcap: float | None = None
+    layers: list[dict[str, Any]] = field(default_factory=list)
+
+    @classmethod
+    def from_dict(cls, raw: dict[str, Any]) -> "GalupelConfig":
+        layers = _need(raw, "layers", list)
+        if not isinstance(layers, list) or not layers:
+            raise ConfigError("config.json key 'layers' must be a list with at least one layer")
+        checked: list[dict[str, Any]] = []
+        for i, layer in enumerate(layers):
+            where = f"layer {i}"
+            kind = layer.get("type") if isinstance(layer, dict) else None
+            if kind not in ("attention", "latent_attention"):
+                raise ConfigError(f"{where}: 'type' must be 'attention' or 'latent_attention', got {kind!r}")
+            mixer = layer.get("mixer")
+            if not isinstance(mixer, dict):
+                raise ConfigError(f"{where}: lacks the object 'mixer'")
+            mask = _opt_object(mixer, "mask", where)
+            if kind == "attention":
+                m: dict[str, Any] = _positive_ints(mixer, ("heads", "kv_heads", "dim", "vdim"), where)
+                if m["heads"] % m["kv_heads"]:
+                    raise ConfigError(f"{where}: heads must be a multiple of kv_heads: {m}")
+                if mask is None or mask.get("size") is None:
+                    raise ConfigError(f"{where}: an 'attention' layer needs mask.size")
+                m["mask"] = _positive_ints(mask, ("size",), where + " mask")
+                if mask.get("pool") is not None:
+                    m["mask"].update(_positive_ints(mask, ("pool",), where + " mask"))
+                if mixer.get("kv_from") is not None:
+                    j = m["kv_from"] = _need(mixer, "kv_from", int)
+                    if not 0 <= j < i or checked[j]["type"] != "attention" or "kv_from" in checked[j]["mixer"]:
+                        raise ConfigError(f"{where}: kv_from must name an earlier 'attention' layer with keys and values of its own, got {j}")
+                    src = checked[j]["mixer"]
+                    if any(src[k] != m[k] for k in ("kv_heads", "dim", "vdim")):
+                        raise ConfigError(f"{where}: layer {j}'s key/value heads and sizes differ from this layer's")
+            else:
+                m = _positive_ints(mixer, ("heads", "dim", "vdim", "kv_rank"), where)
+                m["rot_dim"] = _need(mixer, "rot_dim", int)
+                if m["rot_dim"] < 0:
+                    raise ConfigError(f"{where}: rot_dim must not be negative")
+                rot = _opt_object(mixer, "rot", where)
+                if rot is not None:
+                    m["rot"] = {"base": _need(rot, "base", float), "dims": _need(rot, "dims", int)}
+                    if m["rot"]["dims"] % 2 or not 0 <= m["rot"]["dims"] <= m["rot_dim"] or not m["rot"]["base"] > 0:
+                        raise ConfigError(f"{where}: rot.dims must be even and at most rot_dim, rot.base positive: {m['rot']}")
+                if mask is not None and mask.get("size") is not None:
+                    m["mask"] = _positive_ints(mask, ("size",), where + " mask")
+            m["scale"] = _need(mixer, "scale", float)
+            mlp = layer.get("mlp")
+            if mlp is not None:
+                if not isinstance(mlp, dict) or mlp.get("kind") != "moe":
+                    raise ConfigError(f"{where}: 'mlp' must be null or of kind 'moe', got {mlp!r}")
+                router, expert = mlp.get("router"), mlp.get("expert")
+                if not isinstance(router, dict) or not isinstance(expert, dict):
+                    raise ConfigError(f"{where}: a moe feed-forward needs the objects 'router' and 'expert'")
+                r = _positive_ints(router, ("experts", "top"), where + " mlp.router")
+                groups = _opt_object(router, "groups", where + " mlp.router")
+                r["groups"] = _positive_ints(groups, ("count", "keep"), where + " mlp.router.groups") if groups else {"count": 1, "keep": 1}
+                g = r["groups"]
+                if r["experts"] % g["count"] or g["keep"] > g["count"] or g["keep"] * (r["experts"] // g["count"]) < r["top"]:
+                    raise ConfigError(f"{where}: {g['keep']} of {g['count']} groups over {r['experts']} experts cannot give {r['top']} choices")
+                mlp = {"kind": "moe", "router": r, "expert": _positive_ints(expert, ("ff",), where + " mlp.expert")}
+            checked.append({"type": kind, "mixer": m, "mlp": mlp})
+        norm = raw.get("norm")
+        if not isinstance(norm, dict):
+            raise ConfigError("config.json lacks the object 'norm'")
+        cap = raw.get("logit_softcap")
+        eos = raw.get("eos_token_id", -1)
+        cfg = cls(architecture=architecture_name(raw), vocab_size=_need(raw, "vocab", int), hidden_size=_need(raw, "width", int),
+                  num_hidden_layers=len(checked), max_position_embeddings=int(raw.get("max_position_embeddings", 1 << 30)),
+                  eos_token_id=-1 if eos is None else int(eos), norm_eps=_need(norm, "eps", float),
+                  norm_groups=_need(norm, "groups", int) if norm.get("groups") is not None else 1,
+                  logit_scale=_need(raw, "logit_scale", float) if raw.get("logit_scale") is not None else 1.0,
+                  logit_softcap=_need(raw, "logit_softcap", float) if cap is not None else None, layers=checked)
+        if cfg.vocab_size < 1 or cfg.hidden_size < 1:
+            raise ConfigError("vocab and width must be positive")
+        if not cfg.norm_eps > 0:
+            raise ConfigError("norm.eps must be positive")
+        if cfg.norm_groups < 1 or cfg.hidden_size % cfg.norm_groups:
+            raise ConfigError(f"norm.groups must divide width: {cfg.norm_groups} and {cfg.hidden_size}")
+        if cfg.logit_softcap is not None and not cfg.logit_softcap > 0:
+            raise ConfigError("logit_softcap must be positive")
+        return cfg
+
+    def to_json_dict(self) -> dict[str, Any]:
+        d = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
+             "norm": {"eps": self.norm_eps, "groups": self.norm_groups}, "logit_scale": self.logit_scale, "layers": self.layers}
+        if self.logit_softcap is not None:
+            d["logit_softcap"] = self.logit_softcap
+        return d

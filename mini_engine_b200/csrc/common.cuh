@@ -75,6 +75,20 @@ __device__ __forceinline__ float block_sum(float x, float* red /* >= 32 floats o
 // has finished and its writes are visible, and only then touches activations or the cache; it writes
 // nothing before pdl_wait().  pdl_launch_dependents() lets the successor be scheduled.  In a launch
 // without the attribute both are no-ops.
+// Element-wise activations by number (the keys of ops.ACTIVATIONS): the square of relu, gelu in its tanh form, silu, gelu in its
+// exact form z Phi(z).
+enum { ACT_RELU2 = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_GELU_ERF = 3 };
+
+__device__ __forceinline__ float act_apply(float z, int kind) {
+  if (kind == ACT_RELU2) {
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+  }
+  if (kind == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == ACT_GELU_ERF) return 0.5f * z * (1.f + erff(z * 0.7071067811865476f));
+  return z / (1.f + expf(-z));
+}
+
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 

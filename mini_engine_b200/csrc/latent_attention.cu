@@ -5,7 +5,8 @@
 // output in latent space is sum_j p_j c_j, which the value up-projection W_uv,h then takes to the head's values.
 // So the kernels below are multi-query attention with keys of C + R values and values that are the keys' first C.
 // The softmax may have a sink: a learned logit per head that joins the denominator once, with no key and no value.
-// The result may be multiplied by a gate per (token, head).
+// The result may be multiplied by a gate per (token, head).  With a window w a query at position p sees the keys
+// p - w < j <= p only.
 //
 // me_latent_prep: from the packed projections of a token, the unit-RMS latent c (times its weight), the rotary
 // rotation of the shared key part and of every head's rotated query part (pairs (2i, 2i+1), angle = position *
@@ -81,7 +82,7 @@ latent_attn_kernel(const T* __restrict__ q_abs, const T* __restrict__ q_rot, con
                    const int* __restrict__ block_tables, int bt_stride, const int* __restrict__ cu_seqlens,
                    const int* __restrict__ context_lens, const int* __restrict__ tiles, const float* __restrict__ sink,
                    const float* __restrict__ gate, T* __restrict__ out, int T_total, int H, int C, int R, int page_size,
-                   float scale, int hb) {
+                   float scale, int hb, int window) {
   extern __shared__ float smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -120,7 +121,8 @@ latent_attn_kernel(const T* __restrict__ q_abs, const T* __restrict__ q_rot, con
 #pragma unroll
   for (int k = 0; k < MAXC / 8; ++k) acc[k] = 0.f;
 
-  for (int kt = 0; kt < hi; kt += LAT_BK) {
+  const int lo = window > 0 ? max(0, start + q0 - window + 1) / LAT_BK * LAT_BK : 0;   // the first tile some row's window reaches
+  for (int kt = lo; kt < hi; kt += LAT_BK) {
     __syncthreads();
     for (int idx = tid; idx < LAT_BK * Dk; idx += LAT_THREADS) {
       const int jj = idx / Dk, d = idx - jj * Dk;
@@ -140,7 +142,7 @@ latent_attn_kernel(const T* __restrict__ q_abs, const T* __restrict__ q_rot, con
       const int jj = c + 8 * mm, j = kt + jj;
       float dot = 0.f;
       for (int d = 0; d < Dk; ++d) dot = fmaf(Qs[r * ldh + d], Ks[jj * ldh + d], dot);
-      const bool seen = row_ok && j <= p_r && j < L;
+      const bool seen = row_ok && j <= p_r && j < L && (window <= 0 || j > p_r - window);
       s[mm] = seen ? dot * scale : -INFINITY;
       tmax = fmaxf(tmax, s[mm]);
     }
@@ -223,7 +225,7 @@ template <typename T, int MAXC>
 static int launch_latent_attn(const void* q_abs, const void* q_rot, const void* pool, const int* block_tables, int bt_stride,
                               const int* cu_seqlens, const int* context_lens, const int* tiles, int blocks_x,
                               const float* sink, const float* gate, void* out, int T_total, int H, int C, int R,
-                              int page_size, float scale, int hb, size_t smem, cudaStream_t stream) {
+                              int page_size, float scale, int hb, int window, size_t smem, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(latent_attn_kernel<T, MAXC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -232,18 +234,18 @@ static int launch_latent_attn(const void* q_abs, const void* q_rot, const void* 
   }
   me_launch(latent_attn_kernel<T, MAXC>, dim3(blocks_x, (H + hb - 1) / hb), dim3(LAT_THREADS), smem, stream, (const T*)q_abs,
             (const T*)q_rot, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles, sink, gate, (T*)out,
-            T_total, H, C, R, page_size, scale, hb);
+            T_total, H, C, R, page_size, scale, hb, window);
   return 0;
 }
 
 ME_API int me_latent_attention_tile_q() { return LAT_ROWS; }
 
 // q_abs, out: [H, T, C]; q_rot: [T, H, R].  Requests [0, num_decodes) bring one token each and take a block for 16
-// heads; the others are covered by ``tiles`` ([num_tiles, 2] = request, first local query; 16 queries a tile).
+// heads; the others are covered by ``tiles`` ([num_tiles, 2] = request, first local query; 16 queries a tile).  window: 0 = none.
 ME_API int me_latent_attention(const void* q_abs, const void* q_rot, int dtype, const void* pool, const int* block_tables,
                                int bt_stride, const int* cu_seqlens, const int* context_lens, const int* tiles,
                                int num_tiles, int num_decodes, const float* sink, const float* gate, void* out,
-                               int T_total, int H, int C, int R, int page_size, float scale, cudaStream_t stream) {
+                               int T_total, int H, int C, int R, int page_size, float scale, int window, cudaStream_t stream) {
   ME_REQUIRE(H > 0 && C > 0 && R >= 0 && page_size > 0 && T_total >= 0, "me_latent_attention: bad sizes");
   ME_REQUIRE(C <= 512, "me_latent_attention: a latent of %d values is not supported (up to 512)", C);
   ME_REQUIRE(H <= 65535, "me_latent_attention: too many heads");
@@ -258,10 +260,10 @@ ME_API int me_latent_attention(const void* q_abs, const void* q_rot, int dtype, 
     ME_DISPATCH_DTYPE(dtype, T, {
       if (C <= 128)
         rc = launch_latent_attn<T, 128>(q_abs, q_rot, pool, block_tables, bt_stride, cu_seqlens, context_lens, tl, blocks_x,
-                                        sink, gate, out, T_total, H, C, R, page_size, scale, hb, smem, stream);
+                                        sink, gate, out, T_total, H, C, R, page_size, scale, hb, window, smem, stream);
       else
         rc = launch_latent_attn<T, 512>(q_abs, q_rot, pool, block_tables, bt_stride, cu_seqlens, context_lens, tl, blocks_x,
-                                        sink, gate, out, T_total, H, C, R, page_size, scale, hb, smem, stream);
+                                        sink, gate, out, T_total, H, C, R, page_size, scale, hb, window, smem, stream);
     });
     if (rc) return rc;
     ME_LAUNCH_CHECK("me_latent_attention");

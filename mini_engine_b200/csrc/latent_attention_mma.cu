@@ -55,7 +55,7 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
                        const int* __restrict__ context_lens, const int* __restrict__ tiles,
                        const float* __restrict__ sink, const float* __restrict__ gate, bf16* __restrict__ out,
                        float* __restrict__ partial, int T_total, int H, int C, int R, int page_size, float scale_log2,
-                       int gp, int chunks, int keys_per_split, int nbuf) {
+                       int gp, int chunks, int keys_per_split, int nbuf, int window) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   pdl_wait();
   pdl_launch_dependents();
@@ -77,7 +77,9 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
   const int n_tok = min(tq, q_len - q0);
   const int* bt = block_tables + (int64_t)b * bt_stride;
   const int p_lo = start + q0, p_hi = p_lo + n_tok - 1;
-  const int k_begin = PARTIAL ? split * keys_per_split : 0;
+  // with a window the first tile is the one that the window of the first query reaches (tiles stay at multiples of LM_KEYS)
+  const int w_lo = window > 0 ? max(0, p_lo - window + 1) / LM_KEYS * LM_KEYS : 0;
+  const int k_begin = PARTIAL ? w_lo + split * keys_per_split : w_lo;
   const int k_end = PARTIAL ? min(p_hi + 1, k_begin + keys_per_split) : p_hi + 1;
   const int n_tiles = (n_tok > 0 && k_end > k_begin) ? (k_end - k_begin + LM_KEYS - 1) / LM_KEYS : 0;
 
@@ -136,7 +138,8 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
           mma_bf16(s[2 * np + 1], qf, bfr[2], bfr[3]);
         }
       }
-      const bool need_mask = kt + LM_KEYS - 1 > p_lo || kt + LM_KEYS > k_end || n_tok * gp < LM_ROWS || h0 + gp > H;
+      const bool need_mask = kt + LM_KEYS - 1 > p_lo || kt + LM_KEYS > k_end || n_tok * gp < LM_ROWS || h0 + gp > H ||
+                             (window > 0 && kt <= p_hi - window);
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < LM_KEYS / 8; ++i) {
@@ -145,7 +148,7 @@ latent_attn_mma_kernel(const bf16* __restrict__ q_abs, const bf16* __restrict__ 
             const int j = kt + i * 8 + 2 * t4 + (e & 1);
             const int pos = e < 2 ? pos0 : pos1;
             const bool okr = e < 2 ? ok0 : ok1;
-            if (!(okr && j <= pos && j < k_end)) s[i][e] = -INFINITY;
+            if (!(okr && j <= pos && j < k_end && (window <= 0 || j > pos - window))) s[i][e] = -INFINITY;
           }
         }
       }
@@ -309,7 +312,7 @@ ME_API int me_latent_attention_mma_heads_per_block(int H) { return H >= 7 ? 8 : 
 ME_API int me_latent_attention_mma(const void* q_abs, const void* q_rot, const void* pool, const int* block_tables,
                                    int bt_stride, const int* cu_seqlens, const int* context_lens, const int* tiles,
                                    int num_tiles, const float* sink, const float* gate, void* out, int T_total, int H, int C,
-                                   int R, int page_size, float scale, cudaStream_t stream) {
+                                   int R, int page_size, float scale, int window, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   ME_REQUIRE(me_latent_attention_mma_takes(C, R), "me_latent_attention_mma: rows of %d + %d values are not taken", C, R);
   const int gp = me_latent_attention_mma_heads_per_block(H), cc = C > 128 ? 256 : 128, chunks = (C + cc - 1) / cc;
@@ -328,18 +331,19 @@ ME_API int me_latent_attention_mma(const void* q_abs, const void* q_rot, const v
   ME_REQUIRE((H + gp - 1) / gp <= 65535, "me_latent_attention_mma: too many heads");
   me_launch(kernel, dim3(num_tiles, (H + gp - 1) / gp, chunks), dim3(LM_THREADS), smem, stream,
             (const bf16*)q_abs, (const bf16*)q_rot, (const bf16*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles,
-            sink, gate, (bf16*)out, (float*)nullptr, T_total, H, C, R, page_size, scale * LOG2E, gp, chunks, 0, nbuf);
+            sink, gate, (bf16*)out, (float*)nullptr, T_total, H, C, R, page_size, scale * LOG2E, gp, chunks, 0, nbuf, window);
   ME_LAUNCH_CHECK("me_latent_attention_mma");
   return 0;
 }
 
 // Single tokens: requests [0, num_decodes), each cut into ``splits`` ranges of ``keys_per_split`` keys (a multiple of 64);
-// ``partial``: float32 [num_decodes, splits, H, C + 2].
+// ``partial``: float32 [num_decodes, splits, H, C + 2].  With a window (0: none) the ranges are counted from the tile that
+// the request's window reaches first.
 ME_API int me_latent_attention_decode(const void* q_abs, const void* q_rot, const void* pool, const int* block_tables,
                                       int bt_stride, const int* cu_seqlens, const int* context_lens, int num_decodes,
                                       const float* sink, const float* gate, void* out, float* partial, int splits,
                                       int keys_per_split, int T_total, int H, int C, int R, int page_size, float scale,
-                                      cudaStream_t stream) {
+                                      int window, cudaStream_t stream) {
   if (num_decodes == 0) return 0;
   ME_REQUIRE(me_latent_attention_mma_takes(C, R), "me_latent_attention_decode: rows of %d + %d values are not taken", C, R);
   ME_REQUIRE(splits >= 1 && keys_per_split > 0 && keys_per_split % 64 == 0 && partial != nullptr,
@@ -356,7 +360,7 @@ ME_API int me_latent_attention_decode(const void* q_abs, const void* q_rot, cons
   me_launch(latent_attn_mma_kernel<true, 128, 64>, dim3(num_decodes, (H + LM_ROWS - 1) / LM_ROWS, chunks * splits), dim3(LM_THREADS), smem,
             stream, (const bf16*)q_abs, (const bf16*)q_rot, (const bf16*)pool, block_tables, bt_stride, cu_seqlens, context_lens,
             (const int*)nullptr, (const float*)nullptr, (const float*)nullptr, (bf16*)nullptr, partial, T_total, H, C, R, page_size,
-            scale * LOG2E, LM_ROWS, chunks, keys_per_split, 2);
+            scale * LOG2E, LM_ROWS, chunks, keys_per_split, 2, window);
   ME_LAUNCH_CHECK("me_latent_attention_decode");
   me_launch(latent_merge_kernel, dim3(num_decodes, H), dim3(128), 0, stream, (const float*)partial, cu_seqlens, sink, gate,
             (bf16*)out, T_total, H, C, splits);

@@ -2,11 +2,16 @@
 //
 //   me_moe_route    z [T, E] float32 (+ a bias per expert) -> the ``top`` largest logits of every token (ties: the lower index) and the softmax
 //                   over those logits only;
+//   me_moe_route_grouped   the other routing rule: scores s = sigmoid(z); an expert is chosen by s + correction (a learned number per
+//                   expert that steers the choice and nothing else); the experts form ``groups`` equal groups of neighbours, a
+//                   group's score is the sum of its two largest choice scores, and only experts of the ``keep`` best groups can be
+//                   chosen; the weights are the chosen experts' s themselves, not renormalised;
 //   me_moe_sort     the T * top (token, choice) pairs grouped by expert, in token order inside an expert: offsets [E + 1],
 //                   ``sorted`` (pair ids in expert order) and ``place`` (where each pair went);
 //   me_moe_gemm     one product per expert over its rows: rows of A are gathered through ``sorted`` (pair id / top = token)
-//                   or are already in expert order; with ``glu`` the expert's weight holds gate rows then up rows and the
-//                   result is the clamped gated activation of the two products;
+//                   or are already in expert order; with ``glu`` 1 the expert's weight holds gate rows then up rows and the
+//                   result is the clamped gated activation of the two products; ``glu`` 2 + k: activation k of common.cuh on
+//                   the plain product;
 //   me_moe_combine  y_t = sum_k weight[t, k] * rows[place[t * top + k]] (+ a shared expert's output), k in a fixed order.
 //
 // The products here run on the CUDA cores with float32 accumulation in a fixed order (any dtypes, any sizes); bfloat16
@@ -41,6 +46,87 @@ __device__ __forceinline__ void route_token(float* mine, int E, int top, int lan
     __syncwarp();
   }
   for (int k = lane; k < top; k += 32) wgt[k] /= denom;
+}
+
+// The grouped rule for one token: ``mine`` [E] holds the logits and becomes the choice scores, ``score`` [E] the sigmoids,
+// ``gs`` [groups] the groups' scores.  Ties go to the lower index, among groups and among experts.
+__device__ __forceinline__ void route_token_grouped(float* mine, float* score, float* gs, const float* __restrict__ correction, int E,
+                                                    int top, int groups, int keep, int lane, int* __restrict__ idx,
+                                                    float* __restrict__ wgt) {
+  for (int e = lane; e < E; e += 32) {
+    const float sg = 1.0f / (1.0f + expf(-mine[e]));
+    score[e] = sg;
+    mine[e] = sg + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int n = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;        // the two largest of the group
+      for (int e = g * n; e < (g + 1) * n; ++e) {
+        const float v = mine[e];
+        if (v > a) { b = a; a = v; }
+        else if (v > b) b = v;
+      }
+      gs[g] = n > 1 ? a + b : a;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {             // the best group still unmarked gets +inf, so that it is never taken twice
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || (v == best && g < at) || at == 0x7fffffff)) { best = v; at = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+      }
+      if (lane == 0 && at != 0x7fffffff) gs[at] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gs[e / n] != INFINITY) mine[e] = -INFINITY;
+    __syncwarp();
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = mine[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) at = k;                // nothing left to choose from: keep going with a valid index
+    if (lane == 0) {
+      idx[k] = at;
+      wgt[k] = best == -INFINITY ? 0.f : score[at];
+      mine[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+}
+
+__global__ void __launch_bounds__(128)
+moe_route_grouped_kernel(const float* __restrict__ z, const float* __restrict__ correction, int E, int top, int groups, int keep,
+                         int* __restrict__ idx, float* __restrict__ wgt, int T) {
+  extern __shared__ float zs[];               // [warps][2 E + groups]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* mine = zs + warp * (2 * E + groups);
+  for (int e = lane; e < E; e += 32) mine[e] = z[(int64_t)t * E + e];
+  __syncwarp();
+  route_token_grouped(mine, mine + E, mine + 2 * E, correction, E, top, groups, keep, lane, idx + (int64_t)t * top, wgt + (int64_t)t * top);
 }
 
 __global__ void __launch_bounds__(128)
@@ -154,7 +240,7 @@ template <typename TA, typename TW, typename TO, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ a, int64_t a_stride, const int* __restrict__ sorted, int top,
                 const TW* __restrict__ w, int64_t w_expert_stride, const int* __restrict__ offsets, int E, TO* __restrict__ out,
-                int64_t out_stride, int N, int K, float limit, float alpha, float shift) {
+                int64_t out_stride, int N, int K, float limit, float alpha, float shift, int act) {
   __shared__ float As[MG_BM][MG_BK + 1], Ws[MG_BN][MG_BK + 1], Us[GLU ? MG_BN : 1][MG_BK + 1];
   __shared__ int src_row[MG_BM];
   pdl_wait();
@@ -215,6 +301,8 @@ moe_gemm_kernel(const TA* __restrict__ a, int64_t a_stride, const int* __restric
           u = fminf(fmaxf(u, -limit), limit);
         }
         v = g / (1.f + expf(-alpha * g)) * (u + shift);
+      } else if (act >= 0) {
+        v = act_apply(v, act);
       }
       out[(int64_t)r * out_stride + n] = from_f<TO>(v);
     }
@@ -295,6 +383,18 @@ ME_API int me_moe_route_sort(const float* z, const float* bias, int T, int E, in
   return rc ? rc : me_moe_sort(idx, T, top, E, counts, offsets, sorted, place, stream);
 }
 
+ME_API int me_moe_route_grouped(const float* z, const float* correction, int T, int E, int top, int groups, int keep, int* idx,
+                                float* wgt, cudaStream_t stream) {
+  if (T == 0) return 0;
+  ME_REQUIRE(E >= 1 && top >= 1 && top <= E && E <= 2048, "me_moe_route_grouped: %d experts, %d chosen", E, top);
+  ME_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups && keep * (E / groups) >= top,
+             "me_moe_route_grouped: %d of %d groups of %d experts cannot give %d choices", keep, groups, E / (groups > 0 ? groups : 1), top);
+  me_launch(moe_route_grouped_kernel, dim3((T + 3) / 4), dim3(128), sizeof(float) * 4 * (2 * E + groups), stream, z, correction, E, top,
+            groups, keep, idx, wgt, T);
+  ME_LAUNCH_CHECK("me_moe_route_grouped");
+  return 0;
+}
+
 int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top, const void* w, int64_t w_expert_stride,
                     const int* offsets, int E, void* out, int out_dtype, int64_t out_stride, int rows, int N, int K, int glu,
                     float limit, float alpha, float shift, cudaStream_t stream);
@@ -312,12 +412,12 @@ ME_API int me_moe_gemm(const void* a, int a_dtype, int64_t a_stride, const int* 
                            limit, alpha, shift, stream);
   dim3 grid((rows + MG_BM - 1) / MG_BM + E, (N + MG_BN - 1) / MG_BN);
   ME_DISPATCH_DTYPE(a_dtype, TA, ME_DISPATCH_DTYPE(w_dtype, TW, ME_DISPATCH_DTYPE(out_dtype, TO, {
-    if (glu)
+    if (glu == 1)
       me_launch(moe_gemm_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream, (const TA*)a, a_stride, sorted, top, (const TW*)w,
-                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
+                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift, glu >= 2 ? glu - 2 : -1);
     else
       me_launch(moe_gemm_kernel<TA, TW, TO, false>, grid, dim3(256), 0, stream, (const TA*)a, a_stride, sorted, top, (const TW*)w,
-                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
+                w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift, glu >= 2 ? glu - 2 : -1);
   })));
   ME_LAUNCH_CHECK("me_moe_gemm");
   return 0;

@@ -21,7 +21,7 @@ template <typename TO, bool GLU>
 __global__ void __launch_bounds__(MM_THREADS)
 moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __restrict__ sorted, int top,
                     const bf16* __restrict__ w, int64_t w_expert_stride, const int* __restrict__ offsets, int E,
-                    TO* __restrict__ out, int64_t out_stride, int N, int K, float limit, float alpha, float shift) {
+                    TO* __restrict__ out, int64_t out_stride, int N, int K, float limit, float alpha, float shift, int act) {
   extern __shared__ __align__(16) unsigned char mm_smem[];
   constexpr int HALVES = GLU ? 2 : 1;
   typedef bf16 (*ATile)[MM_BM][MM_LD];
@@ -120,6 +120,8 @@ moe_gemm_mma_kernel(const bf16* __restrict__ a, int64_t a_stride, const int* __r
           up = fminf(fmaxf(up, -limit), limit);
         }
         v = gt / (1.f + expf(-alpha * gt)) * (up + shift);
+      } else if (act >= 0) {
+        v = act_apply(v, act);
       }
       out[(int64_t)r * out_stride + n] = from_f<TO>(v);
     }
@@ -138,7 +140,7 @@ int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top,
   ME_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && w_expert_stride % 8 == 0,
              "me_moe_gemm: operands of the tensor-core kernel must be 16-byte aligned");
   dim3 grid((rows + MM_BM - 1) / MM_BM + E, (N + MM_BN - 1) / MM_BN);
-  const size_t smem = sizeof(bf16) * MM_STAGES * (MM_BM + (glu ? 2 : 1) * MM_BN) * MM_LD;
+  const size_t smem = sizeof(bf16) * MM_STAGES * (MM_BM + (glu == 1 ? 2 : 1) * MM_BN) * MM_LD;
   ME_DISPATCH_DTYPE(out_dtype, TO, {
     static bool attr_set = false;
     if (!attr_set) {
@@ -147,12 +149,12 @@ int me_moe_gemm_mma(const void* a, int64_t a_stride, const int* sorted, int top,
       ME_REQUIRE(e1 == cudaSuccess && e2 == cudaSuccess, "me_moe_gemm: cannot raise shared memory");
       attr_set = true;
     }
-    if (glu)
+    if (glu == 1)
       me_launch(moe_gemm_mma_kernel<TO, true>, grid, dim3(MM_THREADS), smem, stream, (const bf16*)a, a_stride, sorted, top,
-                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
+                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift, glu >= 2 ? glu - 2 : -1);
     else
       me_launch(moe_gemm_mma_kernel<TO, false>, grid, dim3(MM_THREADS), smem, stream, (const bf16*)a, a_stride, sorted, top,
-                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift);
+                (const bf16*)w, w_expert_stride, offsets, E, (TO*)out, out_stride, N, K, limit, alpha, shift, glu >= 2 ? glu - 2 : -1);
   });
   ME_LAUNCH_CHECK("me_moe_gemm (tensor cores)");
   return 0;

@@ -1,0 +1,56 @@
+// Pooled blocks of keys and values: beside the paged cache of a token's keys and values, a second paged cache holds one
+// row for every block of P consecutive tokens, the mean of the block's P keys and the mean of its P values as the first
+// cache holds them (block b = positions bP .. bP + P - 1).  An attention whose window has moved past a block sees the
+// block's row in place of its tokens.
+//
+// me_pool_kv runs behind the cache write of a step: every token of the step whose position ends a block (p + 1 a
+// multiple of P) has its block's rows formed, from keys and values of this step and of earlier ones alike, so the cache
+// must still hold the P - 1 tokens in front of it.  Sums are float32, taken in the order of the positions.
+// One block of threads = one token x one kv head.
+#include "common.cuh"
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+pool_kv_kernel(const T* __restrict__ pool, const int* __restrict__ block_tables, int bt_stride, T* __restrict__ pooled,
+               const int* __restrict__ pooled_tables, int pbt_stride, const int* __restrict__ positions,
+               const int* __restrict__ token_req, int P, int nkv, int D, int Dv, int HD, int page_size) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, kvh = blockIdx.y;
+  const int p = positions[t];
+  if (p < 0 || (p + 1) % P != 0) return;
+  const int req = token_req[t];
+  const int b = (p + 1) / P - 1;
+  const int* bt = block_tables + (int64_t)req * bt_stride;
+  const int dst_page = pooled_tables[(int64_t)req * pbt_stride + b / page_size];
+  if (dst_page < 0) return;
+  const int64_t plane = (int64_t)nkv * page_size * HD;
+  T* dst = pooled + (((int64_t)dst_page * 2 * nkv + kvh) * page_size + (b % page_size)) * HD;
+  const float inv = 1.0f / (float)P;
+  for (int d = threadIdx.x; d < D + Dv; d += blockDim.x) {
+    const bool is_k = d < D;
+    float sum = 0.f;
+    for (int j = p + 1 - P; j <= p; ++j) {
+      const int page = bt[j / page_size];
+      if (page < 0) continue;
+      const int64_t at = (((int64_t)page * 2 * nkv + kvh) * page_size + (j % page_size)) * HD;
+      sum += to_f<T>(is_k ? pool[at + d] : pool[at + plane + d - D]);
+    }
+    if (is_k) dst[d] = from_f<T>(sum * inv);
+    else dst[plane + d - D] = from_f<T>(sum * inv);
+  }
+}
+
+// pool, pooled: [pages][2][nkv][page_size][HD] of ``dtype`` (keys fill the first D elements of a row, values the first Dv).
+// block_tables / pooled_tables: [requests, stride] int32 pages of the two caches.  positions, token_req: [T] int32.
+ME_API int me_pool_kv(const void* pool, const int* block_tables, int bt_stride, void* pooled, const int* pooled_tables,
+                      int pbt_stride, const int* positions, const int* token_req, int dtype, int T, int P, int nkv, int D, int Dv,
+                      int HD, int page_size, cudaStream_t stream) {
+  if (T == 0) return 0;
+  ME_REQUIRE(T > 0 && P >= 1 && nkv >= 1 && nkv <= 65535 && D >= 1 && Dv >= 1 && HD >= D && HD >= Dv && page_size >= 1,
+             "me_pool_kv: bad sizes P=%d kv heads=%d D=%d Dv=%d HD=%d", P, nkv, D, Dv, HD);
+  ME_DISPATCH_DTYPE(dtype, TT, me_launch(pool_kv_kernel<TT>, dim3(T, nkv), dim3(128), 0, stream, (const TT*)pool, block_tables, bt_stride,
+                                         (TT*)pooled, pooled_tables, pbt_stride, positions, token_req, P, nkv, D, Dv, HD, page_size));
+  ME_LAUNCH_CHECK("me_pool_kv");
+  return 0;
+}

@@ -15,6 +15,11 @@
 // elements of its row, a value the first Dv of its own.  Key tiles start at multiples of SA_BK counted from position 0, so the
 // order of a query's sums does not depend on how the prompt was cut or on what shares the batch.
 //
+// Pooled blocks (``pool_p`` = P > 0, with a window w): a second cache of the same layout holds one row per block of P tokens
+// (the mean of the block's keys, the mean of its values; pooled_kv.cu); a query at position p sees, beside the keys of its
+// window, the rows of the blocks that lie wholly in front of the window, (b + 1) P <= p - w + 1, in the same softmax.  The
+// pooled rows are visited first, in tiles counted from block 0.
+//
 // One block = 16 queries of one request x one query head; 128 threads; thread (r, c) owns row r = tid / 8, keys
 // c, c+8, c+16, c+24 of a tile and output elements c, c+8, ...
 #include "common.cuh"
@@ -27,7 +32,8 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
                  T* __restrict__ out, int64_t out_stride, const T* __restrict__ pool, const int* __restrict__ block_tables,
                  int bt_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
                  const int* __restrict__ tiles, int nh, int nkv, int D, int Dv, int HD, int page_size, float scale, int window,
-                 int sink, const float* __restrict__ sinks, float softcap, int keep_first, int chunk) {
+                 int sink, const float* __restrict__ sinks, float softcap, int keep_first, int chunk,
+                 const T* __restrict__ pooled, const int* __restrict__ pooled_tables, int pbt_stride, int pool_p) {
   extern __shared__ float smem[];
   pdl_wait();
   pdl_launch_dependents();
@@ -64,18 +70,28 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
 #pragma unroll
   for (int k = 0; k < SA_MAX / 8; ++k) acc[k] = 0.f;
 
-  for (int kt = keep_hi > 0 ? 0 : lo; kt < hi; kt += SA_BK) {
-    if (kt >= keep_hi && kt < lo) kt = lo;
+  // blocks [0, pooled_hi) can be seen by some row of the tile: those in front of the window of its last row
+  const int pooled_hi = (pool_p > 0 && window > 0) ? max(0, (start + q0 + rows - window) / pool_p) : 0;
+  const int nb_r = (pool_p > 0 && window > 0 && p_r - window + 1 > 0) ? (p_r - window + 1) / pool_p : 0;   // blocks this row sees
+  const int* pbt = pooled_tables ? pooled_tables + (int64_t)b * pbt_stride : nullptr;
+
+  for (int phase = pooled_hi > 0 ? 0 : 1; phase < 2; ++phase) {
+  const bool blocks = phase == 0;             // the tile's rows are pooled blocks, not tokens
+  const int end = blocks ? pooled_hi : hi;
+  const T* src = blocks ? pooled : pool;
+  const int* table = blocks ? pbt : bt;
+  for (int kt = blocks ? 0 : (keep_hi > 0 ? 0 : lo); kt < end; kt += SA_BK) {
+    if (!blocks && kt >= keep_hi && kt < lo) kt = lo;
     __syncthreads();                          // previous tile fully consumed (and Q stored)
     for (int idx = tid; idx < SA_BK * row_len; idx += SA_THREADS) {
       const int jj = idx / row_len, d = idx - jj * row_len;
       const int j = kt + jj;
       float v = 0.f;
-      if (j < hi) {
-        const int page = bt[j / page_size];
+      if (j < end) {
+        const int page = table[j / page_size];
         if (page >= 0) {
           const int64_t at = (((int64_t)page * 2 * nkv + kvh) * page_size + (j % page_size)) * HD;
-          v = to_f<T>(d < D ? pool[at + d] : pool[at + plane + d - D]);
+          v = to_f<T>(d < D ? src[at + d] : src[at + plane + d - D]);
         }
       }
       if (d < D) Ks[jj * ldk + d] = v;
@@ -90,7 +106,7 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(Qs[r * ldk + d], Ks[jj * ldk + d], dot);
       const bool in_mask = chunk > 0 ? j / chunk == p_r / chunk : (window <= 0 || j > p_r - window || j < keep_first);
-      const bool seen = row_ok && j <= p_r && j < L && in_mask;
+      const bool seen = blocks ? (row_ok && j < nb_r) : (row_ok && j <= p_r && j < L && in_mask);
       dot *= scale;
       if (softcap > 0.f) dot = softcap * tanhf(dot / softcap);
       s[mm] = seen ? dot : -INFINITY;
@@ -127,6 +143,7 @@ sink_attn_kernel(const T* __restrict__ q, int64_t q_stride, const float* __restr
       }
     }
   }
+  }
   if (row_ok) {
     const float inv = l > 0.f ? 1.0f / l : 0.f;
     const int64_t t = tok0 + q0 + r;
@@ -149,14 +166,18 @@ ME_API int me_sink_attn_tile_q() { return SA_BQ; }
 // q: [T, nh*D]; gate: float32 [T, >= nh*Dv] pre-activations or null; out: [T, nh*Dv]; pool: [pages][2][nkv][page_size][HD].
 // tiles: [num_tiles, 2] (request, first local query) for requests that bring several tokens; the first num_decodes
 // requests bring one token each and get one block per head.  sinks: [nh] float32 or null; softcap, keep_first, chunk: 0 = none.
+// pooled, pooled_tables: the cache of pooled blocks (same layout and dtype) and its block tables, with pool_p tokens a block; null and 0: none.
 ME_API int me_sink_attn(const void* q, int dtype, int64_t q_stride, const float* gate, int64_t gate_stride, void* out,
                         int64_t out_stride, const void* pool, const int* block_tables, int bt_stride, const int* cu_seqlens,
                         const int* context_lens, const int* tiles, int num_tiles, int num_decodes, int nh, int nkv, int D, int Dv,
                         int HD, int page_size, float scale, int window, int sink, const float* sinks, float softcap,
-                        int keep_first, int chunk, cudaStream_t stream) {
+                        int keep_first, int chunk, const void* pooled, const int* pooled_tables, int pbt_stride, int pool_p,
+                        cudaStream_t stream) {
   ME_REQUIRE(D >= 1 && D <= SA_MAX && Dv >= 1 && Dv <= SA_MAX, "me_sink_attn: key size %d / value size %d beyond %d", D, Dv, SA_MAX);
   ME_REQUIRE(HD >= D && HD >= Dv, "me_sink_attn: cache rows of %d elements are too short", HD);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0 && nh <= 65535, "me_sink_attn: %d heads, %d kv heads", nh, nkv);
+  ME_REQUIRE(pool_p == 0 || (pool_p > 0 && pooled && pooled_tables && window > 0 && chunk == 0 && keep_first == 0),
+             "me_sink_attn: pooled blocks of %d tokens need their cache and a plain window", pool_p);
   const size_t smem = sizeof(float) * ((size_t)(SA_BQ + SA_BK) * (D + 1) + (size_t)SA_BK * (Dv + 1) + SA_BQ * (SA_BK + 1));
   ME_DISPATCH_DTYPE(dtype, T, {
     static bool attr_set = false;
@@ -168,11 +189,11 @@ ME_API int me_sink_attn(const void* q, int dtype, int64_t q_stride, const float*
     if (num_decodes > 0)
       me_launch(sink_attn_kernel<T>, dim3(num_decodes, nh), dim3(SA_THREADS), smem, stream, (const T*)q, q_stride, gate, gate_stride,
                 (T*)out, out_stride, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, (const int*)nullptr, nh, nkv,
-                D, Dv, HD, page_size, scale, window, sink, sinks, softcap, keep_first, chunk);
+                D, Dv, HD, page_size, scale, window, sink, sinks, softcap, keep_first, chunk, (const T*)pooled, pooled_tables, pbt_stride, pool_p);
     if (num_tiles > 0)
       me_launch(sink_attn_kernel<T>, dim3(num_tiles, nh), dim3(SA_THREADS), smem, stream, (const T*)q, q_stride, gate, gate_stride,
                 (T*)out, out_stride, (const T*)pool, block_tables, bt_stride, cu_seqlens, context_lens, tiles, nh, nkv, D, Dv,
-                HD, page_size, scale, window, sink, sinks, softcap, keep_first, chunk);
+                HD, page_size, scale, window, sink, sinks, softcap, keep_first, chunk, (const T*)pooled, pooled_tables, pbt_stride, pool_p);
   });
   ME_LAUNCH_CHECK("me_sink_attn");
   return 0;

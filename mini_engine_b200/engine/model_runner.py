@@ -70,7 +70,8 @@ def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, t
     for slot, needs in enumerate(model.slot_needs):
         for need in needs:
             if isinstance(need, KVCacheNeed):
-                keyed.setdefault((need.window, need.num_kv_heads, need.head_dim, need.planes, need.keep_first, need.chunk), []).append(slot)
+                key = (need.window, need.num_kv_heads, need.head_dim, need.planes, need.keep_first, need.chunk, need.every)
+                keyed.setdefault(key, []).append((slot, need.name))
             elif isinstance(need, StateNeed):
                 if any(n.name == need.name for n in states.get(slot, [])):
                     raise ValueError(f"cache slot {slot}: two states are named {need.name!r}")
@@ -78,10 +79,13 @@ def plan_cache_groups(model: DecoderModel) -> tuple[list[GroupSpec], dict[int, t
             else:
                 raise TypeError(f"cache slot {slot}: unknown kind of cache need {need!r}")
     groups, location = [], {}
-    for (window, nkv, hd, planes, keep_first, chunk), slots in keyed.items():
-        for i, s in enumerate(slots):
-            location[s] = (len(groups), i)
-        groups.append(GroupSpec(window, nkv, hd, tuple(slots), planes, keep_first, chunk))
+    for (window, nkv, hd, planes, keep_first, chunk, every), slots in keyed.items():
+        for i, (s, name) in enumerate(slots):
+            where = s if not name else (s, name)          # a layer's second cache is found by (slot, name)
+            if where in location:
+                raise ValueError(f"cache slot {s}: two caches are named {name!r}")
+            location[where] = (len(groups), i)
+        groups.append(GroupSpec(window, nkv, hd, tuple(s for s, _ in slots), planes, keep_first, chunk, every))
     return groups, location, states
 
 
@@ -363,11 +367,14 @@ class ModelRunner:
             sm = host[o_sm[g]:o_sm[g] + T]
             sm[:] = -1
             t = 0
+            by_token = self.groups[g].every == 1       # a cache with a row per block of tokens is written by its own kernel
             for k, i in enumerate(order):
                 holder = items[i].holder
                 table = holder.table_array(g) if hasattr(holder, "table_array") else \
                     np.asarray(holder.block_tables[g], dtype=np.int32)
                 bt[k, :len(table)] = table
+                if not by_token:
+                    continue
                 if lens[k] == 1:
                     pos = starts[k]
                     pi = pos // ps

@@ -104,8 +104,9 @@ class StepContext:
         self._views[key] = (flat, view)              # the same tensor object until the storage is replaced
         return view
 
-    def kv_cache(self, cache_slot: int) -> KVView:
-        g, idx = self.runner.slot_location[cache_slot]
+    def kv_cache(self, cache_slot: int, name: str = "") -> KVView:
+        """``name``: which cache, for a layer that asked for several (``KVCacheNeed.name``)."""
+        g, idx = self.runner.slot_location[cache_slot if not name else (cache_slot, name)]
         return KVView(self.runner.kv_pools[g][idx], self.runner.page_size, self._bt[g], self._sm[g], g)
 
     def state(self, cache_slot: int, name: str = "") -> torch.Tensor:

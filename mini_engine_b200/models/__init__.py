@@ -1,2 +1,2 @@
 """Built-in architectures; importing this package registers them."""
-from . import gevulorn, logozen, pugadra, qwen3  # noqa: F401
+from . import galupel, gevulorn, logozen, pugadra, qwen3  # noqa: F401

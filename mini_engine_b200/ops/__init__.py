@@ -29,10 +29,10 @@ _PROTOS = {
     "me_mlstm_scan": [_P, _L, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "me_mlstm_out": [_P, _P, _L, _I, _P, _F, _P, _I, _I, _I, _I, _I, _I, _P],
     "me_latent_prep": [_P, _L, _I, _I, _I, _P, _F, _P, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    "me_latent_attention": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
+    "me_latent_attention": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_heads_to_rows": [_P, _P, _I, _I, _I, _I, _P],
-    "me_latent_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _P],
-    "me_latent_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+    "me_latent_attention_mma": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    "me_latent_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_add_rmsnorm": [_P, _P, _I, _P, _F, _P, _I, _P, _I, _I, _I, _L, _P],
     "me_gemm_skinny": [_P, _L, _P, _P, _I, _L, _P, _I, _I, _I, _I, _P],
     "me_silu_mul": [_P, _P, _I, _I, _I, _P],
@@ -56,15 +56,18 @@ _PROTOS = {
     "me_clamped_glu": [_P, _I, _L, _P, _I, _L, _I, _I, _F, _F, _F, _P],
     "me_conv_rope_kv": [_P, _L, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     "me_rope_table": [_P, _P, _I, _I, _P, _P],
-    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _I, _I, _P],
+    "me_sink_attn": [_P, _I, _L, _P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P, _F, _I, _I, _P, _P, _I, _I, _P],
     "me_parallel_norm": [_P, _P, _P, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _F, _P],
-    "me_attn_prep": [_P, _L, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_attn_prep": [_P, _L, _P, _P, _P, _I, _F, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P],
     "me_gla_decay": [_P, _L, _I, _I, _P, _I, _P, _F, _P, _I, _I, _P],
     "me_gla_scan": [_P, _L, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P, _P],
     "me_activation": [_P, _I, _L, _P, _I, _L, _I, _I, _I, _P],
-    "me_soft_cap": [_P, _L, _F, _P],
+    "me_soft_cap": [_P, _L, _F, _F, _P],
     "me_add_row_vector": [_P, _I, _I, _I, _P, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
+    "me_moe_route_grouped": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
+    "me_group_norm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
+    "me_pool_kv": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _F, _I, _P],
@@ -1215,11 +1218,13 @@ def latent_prep(proj: torch.Tensor, offsets: dict, c_weight: torch.Tensor, eps: 
 
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, page_size: int, block_tables: torch.Tensor,
-                     meta, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor, scale: float) -> None:
+                     meta, sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor, scale: float,
+                     window: Optional[int] = None) -> None:
     """Causal multi-query attention over cache rows [c | rotated key part]: ``q_abs`` [H, T, C] against c, ``q_rot``
     [T, H, R] against the rest; ``out`` [H, T, C] = softmax-weighted sum of c (with ``sink`` [H] in the denominator),
-    times ``gate`` [T, H]."""
+    times ``gate`` [T, H].  ``window``: a query at position p sees the keys p - window < j <= p only."""
     H, T, C = q_abs.shape
+    window = int(window or 0)
     R = q_rot.shape[2]
     _need(q_abs.is_contiguous() and q_rot.is_contiguous() and out.is_contiguous() and out.shape == q_abs.shape, "latent_attention: shapes")
     _need(pool.shape[-1] == C + R and pool.dtype == q_abs.dtype, "latent_attention: cache rows")
@@ -1232,18 +1237,19 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tenso
                   meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr())
         if n_tiles:
             _call("me_latent_attention_mma", *common, tiles.data_ptr(), n_tiles, _ptr(sink), _ptr(gate), out.data_ptr(), T, H, C, R,
-                  page_size, float(scale), _stream())
+                  page_size, float(scale), window, _stream())
         D = meta.num_decodes
         if D:
-            splits, keys = latent_decode_plan(D, H, C, meta.max_context_len)
+            # (with a window a request's ranges start at the tile its window reaches first)
+            splits, keys = latent_decode_plan(D, H, C, min(meta.max_context_len, window + 63) if window else meta.max_context_len)
             partial = meta.workspace("latent_partials", (D, splits, H, C + 2), torch.float32)
             _call("me_latent_attention_decode", *common, D, _ptr(sink), _ptr(gate), out.data_ptr(), partial.data_ptr(), splits, keys,
-                  T, H, C, R, page_size, float(scale), _stream())
+                  T, H, C, R, page_size, float(scale), window, _stream())
         return
     tiles, n_tiles = meta.tile_lists[LATENT_TILE_Q]
     _call("me_latent_attention", q_abs.data_ptr(), q_rot.data_ptr(), _dt(q_abs), pool.data_ptr(), block_tables.data_ptr(),
           block_tables.stride(0), meta.cu_seqlens.data_ptr(), meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles,
-          meta.num_decodes, _ptr(sink), _ptr(gate), out.data_ptr(), T, H, C, R, page_size, float(scale), _stream())
+          meta.num_decodes, _ptr(sink), _ptr(gate), out.data_ptr(), T, H, C, R, page_size, float(scale), window, _stream())
 
 
 def heads_to_rows(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -1264,6 +1270,40 @@ def batched_heads_mm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> Non
     with _Timed("library_bmm"):
         torch.bmm(x, w, out=out)
     library_calls += 1
+
+
+# ---- a norm behind the sub-layer, in groups; pooled blocks of keys and values -------------------------------------------------
+def group_norm(residual: torch.Tensor, y: Optional[torch.Tensor], weight: torch.Tensor, groups: int, eps: float,
+               out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> None:
+    """RMS norm in ``groups`` equal consecutive parts of a row, each divided by its own sqrt(mean(part^2) + eps), times ``weight``.
+    With ``y``: ``residual += norm(y)``; without: ``residual <- norm(residual)``; ``out`` (optional) receives the new rows of the
+    float32 stream in its own dtype.  With ``rows``: ``out[i] = norm(residual[rows[i]])`` and the stream is left alone."""
+    T, W = residual.shape
+    n = T if rows is None else rows.shape[0]
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and weight.dtype == torch.float32 and weight.numel() == W,
+          "group_norm: a float32 stream [T, W] and a float32 weight [W]")
+    _need(groups >= 1 and W % groups == 0, f"group_norm: {W} values do not split into {groups} groups")
+    _need(y is None or (rows is None and y.shape[0] == T and y.shape[1] >= W and y.stride(1) == 1), "group_norm: the output's rows")
+    _need(out is None or (out.is_contiguous() and tuple(out.shape) == (n, W)), "group_norm: the copy's shape")
+    _need(rows is None or (rows.dtype == torch.int32 and out is not None), "group_norm: int32 rows and a place for them")
+    _call("me_group_norm", residual.data_ptr(), _ptr(y), _dt(y) if y is not None else 0, y.stride(0) if y is not None else 0,
+          weight.data_ptr(), int(groups), float(eps), _ptr(out), _dt(out) if out is not None else 0, _ptr(rows), n, W, _stream())
+
+
+def pool_kv(pool: torch.Tensor, block_tables: torch.Tensor, pooled: torch.Tensor, pooled_tables: torch.Tensor, positions: torch.Tensor,
+            token_req: torch.Tensor, block: int, dim: int, vdim: int, page_size: int) -> None:
+    """Behind a step's cache write: for every token of the step whose position ends a block of ``block`` tokens, the mean of the
+    block's keys and the mean of its values (as ``pool`` holds them) go to row position // block of ``pooled``, a cache of the
+    same layout with block tables of its own (see csrc/pooled_kv.cu)."""
+    T = positions.numel()
+    _need(pool.dim() == 5 and pool.shape[1] == 2 and pool.is_contiguous() and pooled.is_contiguous() and pooled.dtype == pool.dtype
+          and pooled.shape[1:] == pool.shape[1:], "pool_kv: both caches are [pages, 2, kv heads, page, row] of one dtype")
+    _need(block_tables.dtype == pooled_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and pooled_tables.stride(1) == 1,
+          "pool_kv: block tables")
+    _need(token_req.numel() == T and block >= 1, "pool_kv: a request for every token and a block size")
+    _call("me_pool_kv", pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), pooled.data_ptr(), pooled_tables.data_ptr(),
+          pooled_tables.stride(0), positions.data_ptr(), token_req.data_ptr(), _dt(pool), T, int(block), pool.shape[2], dim, vdim,
+          pool.shape[-1], page_size, _stream())
 
 
 # ---- norms on both sides of a sub-layer, convolved and gated attention with a sink, routed feed-forwards ----------------
@@ -1315,7 +1355,7 @@ def parallel_norm(residual: torch.Tensor, adds: Sequence[torch.Tensor], vectors:
           float(eps), _stream())
 
 
-ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2}
+ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2, "gelu": 3}     # "gelu": the exact form, z Phi(z)
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
@@ -1326,10 +1366,15 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
     _call("me_activation", x.data_ptr(), _dt(x), x.stride(0), out.data_ptr(), _dt(out), out.stride(0), T, F, ACTIVATIONS[kind], _stream())
 
 
-def soft_cap(x: torch.Tensor, cap: float) -> None:
-    """``x <- cap * tanh(x / cap)`` in place (float32)."""
-    _need(x.dtype == torch.float32 and x.is_contiguous() and cap > 0, "soft_cap: float32 values and a positive cap")
-    _call("me_soft_cap", x.data_ptr(), x.numel(), float(cap), _stream())
+def _activation_in_place(x: torch.Tensor, kind: str) -> None:
+    _call("me_activation", x.data_ptr(), _dt(x), x.stride(0), x.data_ptr(), _dt(x), x.stride(0), x.shape[0], x.shape[1], ACTIVATIONS[kind],
+          _stream())
+
+
+def soft_cap(x: torch.Tensor, cap: Optional[float], scale: float = 1.0) -> None:
+    """``x <- cap * tanh(scale * x / cap)`` in place (float32); without a cap ``x <- scale * x``."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and (cap is None or cap > 0), "soft_cap: float32 values and a positive cap")
+    _call("me_soft_cap", x.data_ptr(), x.numel(), float(cap or 0.0), float(scale), _stream())
 
 
 def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> None:
@@ -1342,17 +1387,23 @@ def add_row_vector(x: torch.Tensor, v: torch.Tensor) -> None:
 def attn_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
               norm: Optional[str], eps: float, freq: Optional[torch.Tensor], positions: torch.Tensor,
               slot_mapping: Optional[torch.Tensor], q_out: torch.Tensor, pool: Optional[torch.Tensor], page_size: int,
-              num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> None:
-    """From the packed float32 projections q|k|v (the leading columns of ``proj``): bias, a weighted RMS norm of every q and k
+              num_heads: int, num_kv_heads: int, dim: int, vdim: int, q_scale: Optional[torch.Tensor] = None,
+              own_kv: bool = True) -> None:
+    """From the packed float32 projections q|k|v (the leading columns of ``proj``; q alone with ``own_kv`` False): bias, a weighted RMS norm of every q and k
     head in front of the rotation (``norm`` "before") or a plain one behind it ("after"), the rotation of element i with
     element i + len(freq) by position x ``freq`` (float64 frequencies), queries to ``q_out`` and keys and values into the
-    cache rows that ``slot_mapping`` names (see csrc/attn_prep.cu)."""
+    cache rows that ``slot_mapping`` names (see csrc/attn_prep.cu).  ``q_scale`` (float32 [heads]): every query head is
+    multiplied by its number at the end."""
     T = proj.shape[0]
-    C = num_heads * dim + num_kv_heads * (dim + vdim)
+    C = num_heads * dim + (num_kv_heads * (dim + vdim) if own_kv else 0)
+    _need(own_kv or slot_mapping is None, "attn_prep: a mixer without keys and values of its own writes no cache rows")
+    _need(q_scale is None or (q_scale.dtype == torch.float32 and q_scale.numel() == num_heads and q_scale.is_contiguous()),
+          "attn_prep: q_scale must be float32 [heads]")
     _need(norm in (None, "before", "after"), "attn_prep: norm is None, 'before' or 'after'")
     _need(proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= C, "attn_prep: projections must be float32 rows")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == C), "attn_prep: bias must be float32 [channels]")
-    _need(norm != "before" or all(w is not None and w.dtype == torch.float32 and w.numel() == dim for w in (q_norm, k_norm)),
+    _need(norm != "before" or all(w is not None and w.dtype == torch.float32 and w.numel() == dim
+                                  for w in ((q_norm, k_norm) if own_kv else (q_norm,))),
           "attn_prep: the norm in front of the rotation needs float32 weights [dim]")
     _need(freq is None or (freq.dtype == torch.float64 and freq.is_contiguous() and 2 * freq.numel() <= dim), "attn_prep: freq must be float64 [<= dim / 2]")
     _need(q_out.is_contiguous() and tuple(q_out.shape) == (T, num_heads * dim), "attn_prep: query output shape")
@@ -1362,7 +1413,8 @@ def attn_prep(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional
     rot = 2 * freq.numel() if freq is not None else 0
     _call("me_attn_prep", proj.data_ptr(), proj.stride(0), _ptr(bias), _ptr(q_norm), _ptr(k_norm), {None: 0, "before": 1, "after": 2}[norm],
           float(eps), _ptr(freq) if rot else 0, rot, positions.data_ptr(), _ptr(slot_mapping), q_out.data_ptr(), _ptr(pool), _dt(q_out),
-          pool.shape[-1] if pool is not None else 0, page_size, num_heads, num_kv_heads, dim, vdim, T, _stream())
+          pool.shape[-1] if pool is not None else 0, page_size, num_heads, num_kv_heads, dim, vdim, T, _ptr(q_scale), 1 if own_kv else 0,
+          _stream())
 
 
 def clamped_glu(x: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float = 1.0) -> None:
@@ -1422,13 +1474,15 @@ use_sink_attention_mma = True     # bfloat16 attention with a sink on the tensor
 def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, pool: torch.Tensor, page_size: int,
                    block_tables: torch.Tensor, meta, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
                    window: Optional[int], sink: bool, sinks: Optional[torch.Tensor] = None, softcap: Optional[float] = None,
-                   keep_first: int = 0, chunk: Optional[int] = None) -> None:
+                   keep_first: int = 0, chunk: Optional[int] = None, pooled: Optional[tuple] = None) -> None:
     """Attention over the paged cache with keys of ``dim`` and values of ``vdim`` elements: ``q`` [T, heads * dim] -> ``out``
     [T, heads * vdim]; a query at position p sees keys p - window < j <= p; with ``sink`` the softmax's denominator has one
     more term, exp(0); ``gate`` (float32 rows of pre-activations, heads * vdim wide) multiplies the output by its sigmoid.
     ``sinks`` (float32 [heads]): the term is exp(sinks[head]) instead; ``softcap`` c: scores become c tanh(s / c) after the
     scale; ``keep_first``: the window also shows keys j < keep_first; ``chunk`` (instead of a window): a query sees the keys
-    j <= p with floor(j / chunk) = floor(p / chunk).
+    j <= p with floor(j / chunk) = floor(p / chunk).  ``pooled`` = (cache, block tables, P): a second cache of the same layout
+    with one row per block of P tokens (``pool_kv``); beside its window a query sees the rows of the blocks that lie wholly in
+    front of the window, (b + 1) P <= p - window + 1, in the same softmax.
 
     bfloat16 with keys and values of 64 or 128 elements (the cache row's size) runs the engine's tensor-core kernels, the
     tcgen05 one for portions of prompts and the split-K one for single tokens; everything else the CUDA-core kernel of
@@ -1446,8 +1500,15 @@ def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
           "sink_attention: learned sinks are float32 [heads]")
     _need(not (chunk and window), "sink_attention: a window or chunks, not both")
     masked = bool(softcap or keep_first or chunk)      # what only the kernels fed by tensor-map loads know
+    pool_p = 0
+    if pooled is not None:
+        _need(window and not chunk and not keep_first, "sink_attention: pooled blocks go with a plain window")
+        _need(pooled[0].dtype == pool.dtype and pooled[0].shape[1:] == pool.shape[1:] and pooled[0].is_contiguous()
+              and pooled[1].dtype == torch.int32 and pooled[1].stride(1) == 1 and int(pooled[2]) >= 1,
+              "sink_attention: the pooled cache has the layout and dtype of the cache, int32 tables and a block size")
+        pool_p = int(pooled[2])
     decodes, tiles_left = meta.num_decodes, True
-    fast = (use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
+    fast = (use_sink_attention_mma and pooled is None and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
             and meta.error_flag is not None and q.is_contiguous() and q.data_ptr() % 16 == 0)
     extras = dict(keep_first=keep_first, chunk=chunk or 0, softcap=softcap or 0.0, sinks=sinks)
     if fast and decodes and (not masked or (page_size >= 8 and DECODE_PARTITION % page_size == 0)):
@@ -1466,7 +1527,8 @@ def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
               out.stride(0), pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
               meta.context_lens.data_ptr(), tiles.data_ptr(), n_tiles, decodes, num_heads, num_kv_heads, dim, vdim, HD, page_size,
               float(scale), int(window or 0), 1 if sink else 0, _ptr(sinks), float(softcap or 0.0), int(keep_first or 0),
-              int(chunk or 0), _stream())
+              int(chunk or 0), pooled[0].data_ptr() if pool_p else 0, pooled[1].data_ptr() if pool_p else 0,
+              pooled[1].stride(0) if pool_p else 0, pool_p, _stream())
 
 
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx: torch.Tensor, weights: torch.Tensor) -> None:
@@ -1477,6 +1539,20 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, idx:
     _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
           and idx.is_contiguous() and weights.is_contiguous(), "moe_route: outputs are [T, top]")
     _call("me_moe_route", logits.data_ptr(), _ptr(bias), T, E, top, idx.data_ptr(), weights.data_ptr(), _stream())
+
+
+def moe_route_grouped(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, idx: torch.Tensor,
+                      weights: torch.Tensor) -> None:
+    """Routing by sigmoid scores with a correction that only steers the choice, over groups of neighbouring experts: s =
+    sigmoid(``logits``) [T, E]; choice scores s + ``correction``; a group's score is the sum of its two largest choice scores;
+    the ``top`` best experts of the ``keep`` best groups are chosen (ties: the lower index); ``weights`` are their s."""
+    T, E = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route_grouped: logits must be float32")
+    _need(correction is None or (correction.dtype == torch.float32 and correction.numel() == E), "moe_route_grouped: correction must be float32 [E]")
+    _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
+          and idx.is_contiguous() and weights.is_contiguous(), "moe_route_grouped: outputs are [T, top]")
+    _call("me_moe_route_grouped", logits.data_ptr(), _ptr(correction), T, E, top, int(groups), int(keep), idx.data_ptr(), weights.data_ptr(),
+          _stream())
 
 
 def moe_sort(idx: torch.Tensor, num_experts: int, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor,
@@ -1511,11 +1587,13 @@ MOE_TCGEN05_MIN_ROWS = 512   # (token, choice) pairs from which the experts' pro
 
 
 def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: torch.Tensor, offsets: torch.Tensor,
-             out: torch.Tensor, glu: Optional[tuple] = None, workspace=None, err: Optional[torch.Tensor] = None) -> None:
+             out: torch.Tensor, glu: Optional[tuple] = None, workspace=None, err: Optional[torch.Tensor] = None,
+             activation: Optional[str] = None) -> None:
     """One product per expert: ``weight`` [E, N or 2N, K]; the rows of ``a`` are gathered through ``order`` (pair id // top) or,
     without it, lie in expert order already; ``out`` [pairs, N] in expert order.  ``glu`` = (limit, alpha[, shift]): the weight holds gate
     rows then up rows and the result is the gated activation g sigmoid(alpha g) (u + shift), clamped by a positive limit (shift 1
-    when it is not given).
+    when it is not given).  ``activation`` (a key of ``ACTIVATIONS``, instead of ``glu``): that function of the plain product, in the
+    product's epilogue on the CUDA cores and in the mma.sync kernel, as a pass of its own behind the tcgen05 kernel.
 
     bfloat16 operands with K a multiple of 8 run on the tensor cores: from ``MOE_TCGEN05_MIN_ROWS`` pairs on (and with
     ``workspace`` and ``err`` given) the tcgen05 kernel of csrc/gemm_tcgen05.cu over rows brought into expert order first,
@@ -1526,6 +1604,8 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
     _need(weight.is_contiguous() and a.stride(1) == 1 and a.shape[1] == K and out.stride(1) == 1 and out.shape[1] == N, "moe_gemm: shapes")
     _need(order is not None or a.shape[0] == rows, "moe_gemm: rows in expert order")
     limit, alpha, shift = (tuple(glu) + (1.0,))[:3] if glu else (0.0, 0.0, 0.0)
+    _need(activation is None or (not glu and activation in ACTIVATIONS), "moe_gemm: an activation instead of the gate, by a known name")
+    epi = 1 if glu else (2 + ACTIVATIONS[activation] if activation else 0)
     if (use_moe_mma and use_tcgen05_gemm and workspace is not None and err is not None and rows >= MOE_TCGEN05_MIN_ROWS
             and a.dtype == weight.dtype == torch.bfloat16 and K % 8 == 0 and weight.data_ptr() % 16 == 0
             and (out.dtype == torch.bfloat16 or (not glu and out.dtype == torch.float32))):
@@ -1538,10 +1618,12 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
             _call("me_gemm_tcgen05_grouped", matrix_tensor_map(a, 128).ptr, matrix_tensor_map(weight.view(E * NN, K), bn // 2 if glu else bn).ptr,
                   out.data_ptr(), _dt(out), out.stride(0), offsets.data_ptr(), E, rows, N, NN, K, 1 if glu else 0, float(limit),
                   float(alpha), float(shift), bn, err.data_ptr(), _stream())
+            if activation:
+                _activation_in_place(out, activation)
             return
         order = None
     _call("me_moe_gemm", a.data_ptr(), _dt(a), a.stride(0), _ptr(order), top, weight.data_ptr(), _dt(weight), weight.stride(0),
-          offsets.data_ptr(), E, out.data_ptr(), _dt(out), out.stride(0), rows, N, K, 1 if glu else 0, float(limit), float(alpha),
+          offsets.data_ptr(), E, out.data_ptr(), _dt(out), out.stride(0), rows, N, K, epi, float(limit), float(alpha),
           float(shift), 1 if use_moe_mma else 0, _stream())
 
 

@@ -49,13 +49,18 @@ class KVCacheNeed:
     """Paged keys and values: ``window=None`` keeps every key, else the last ``window``.  ``planes``: 2 for keys and
     values, 1 for a cache with one row per token and head (a latent that serves as both).  ``keep_first``: a window that
     also keeps the sequence's first tokens for good.  ``chunk`` (instead of a window): only the keys of the chunk that is
-    being filled are kept, chunks of this many tokens counted from position 0."""
+    being filled are kept, chunks of this many tokens counted from position 0.  ``every`` > 1: the cache has one row for every
+    ``every`` tokens (row b belongs to positions b * every .. b * every + every - 1: a summary of a block of tokens), so a
+    request of n tokens holds ceil(n / every) rows; such rows are never given back behind a window.  ``name``: a layer may ask
+    for several caches; each then has a name of its own, by which ``StepContext.kv_cache(cache_slot, name)`` finds it."""
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     planes: int = 2
     keep_first: int = 0
     chunk: Optional[int] = None
+    every: int = 1
+    name: str = ""
 
 
 @dataclass(frozen=True)
@@ -86,6 +91,13 @@ class NormedUpdate:
     weight: "torch.Tensor"
     eps: float
     mult: float
+
+
+@dataclass
+class StreamCopy:
+    """What a block whose sub-layers read the residual stream itself returns: nothing is pending (the stream holds every
+    sum), and ``x`` [T, width] is the stream as it stands, in the working dtype, for whoever multiplies it next."""
+    x: "torch.Tensor"
 
 
 @dataclass

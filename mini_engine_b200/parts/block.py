@@ -10,7 +10,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
-from .base import NormedUpdate, ParamDecl, Part, PendingSum, StreamUpdate, Upcoming
+from .base import NormedUpdate, ParamDecl, Part, PendingSum, StreamCopy, StreamUpdate, Upcoming
 from .registry import PartSpec, build_part, register_block
 
 
@@ -279,6 +279,33 @@ class ParallelBlock(Block):
         return pending
 
 
+class PostNormBlock(Block):
+    """A block whose norms sit behind the sub-layers and nowhere else: x <- x + norm1(mixer(x)), then x <- x + norm2(ff(x));
+    the sub-layers read the stream itself, and the feed-forward may be absent.  Nothing is left pending: the norm's kernel adds
+    the normalised output into the float32 stream and hands the new stream on in the working dtype (``StreamCopy``), to the
+    next sub-layer and to the next block.  The norms must be of a kind with ``add_normed`` (``group_rmsnorm``)."""
+    capturable = True
+    feed_forward_optional = True
+
+    def __init__(self, spec: BlockSpec, shared: Optional[dict] = None):
+        super().__init__(spec, shared)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("a 'post_norm' block needs norms that can add a normalised output to the stream (kind 'group_rmsnorm')")
+
+    def forward(self, residual, delta, ctx, call, upcoming=None):
+        if isinstance(delta, StreamCopy):
+            x = delta.x
+        elif delta is None:
+            x = residual if ctx.act_dtype == residual.dtype else residual.to(ctx.act_dtype)
+        else:
+            raise TypeError(f"a 'post_norm' block cannot take a pending {type(delta).__name__} from the block before it")
+        update = self.mixer_norm.add_normed(residual, self.mixer.forward(x, ctx, call), ctx)
+        if self.feed_forward is not None:
+            update = self.feed_forward_norm.add_normed(residual, self.feed_forward.forward(update.x, ctx), ctx)
+        return update
+
+
 @dataclass(frozen=True)
 class SharedRef:
     """Stands in a PartSpec's args for an object that the model builds once and shares."""
@@ -289,3 +316,4 @@ register_block("pre_norm", PreNormBlock)
 register_block("hyper_connection", HyperConnectionBlock)
 register_block("sandwich_norm", SandwichNormBlock)
 register_block("parallel", ParallelBlock)
+register_block("post_norm", PostNormBlock)

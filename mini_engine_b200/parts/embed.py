@@ -37,13 +37,15 @@ class TokenEmbedding(Part):
 class LMHead(Part):
     capturable = True
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None, param: str = "weight", softcap: float | None = None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None, param: str = "weight", softcap: float | None = None,
+                 scale: float = 1.0):
         super().__init__()
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
         self.param = param
         self.softcap = float(softcap) if softcap else None     # logits <- cap * tanh(logits / cap)
+        self.scale = float(scale)                              # ... of the logits times this
 
     def param_decls(self):
         return [ParamDecl(self.param, (self.vocab_size, self.hidden_size), tied_to=self.tied_to)]
@@ -52,6 +54,6 @@ class LMHead(Part):
         out = ctx.buffer("logits", (x.shape[0], self.vocab_size), torch.float32)
         ops.tag = "logits"
         ops.linear(x, self.p(self.param), out, workspace=ctx.buffer, err=ctx.error_flag)
-        if self.softcap:
-            ops.soft_cap(out, self.softcap)
+        if self.softcap or self.scale != 1.0:
+            ops.soft_cap(out, self.softcap, self.scale)
         return out

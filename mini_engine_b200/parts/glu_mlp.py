@@ -8,6 +8,12 @@ is the plain SiLU-gated form silu(g) * u.
 logit, mixed by a softmax taken over those ``top`` logits alone; the output is that mix of their outputs, plus a
 ``shared`` expert (same form, sizes of its own) that runs for every token.  Routing, grouping by expert, the per-expert
 products and the weighted sum all run on the device, so a step's shape does not depend on the routing.
+
+Two more choices.  ``routing`` "sigmoid_groups" (instead of "softmax_top"): scores s = sigmoid(z); the choice is made by
+s + ``correction`` (a learned number per expert that only steers the choice); the experts form ``groups`` = (count, keep)
+equal groups of neighbours, a group's score is the sum of its two largest choice scores, and only experts of the ``keep``
+best groups can be chosen; the weights are the chosen experts' s, not renormalised.  ``activation`` (a key of
+``ops.ACTIVATIONS``, instead of the gate): an expert is W_down act(W_up h) and has no gate matrix.
 """
 from __future__ import annotations
 
@@ -64,15 +70,29 @@ class RoutedExperts(FeedForward):
     capturable = True
 
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, limit: Optional[float] = None,
-                 alpha: float = 1.702, shift: float = 1.0, router_bias: bool = True, shared: Optional[dict] = None):
+                 alpha: float = 1.702, shift: float = 1.0, router_bias: bool = True, shared: Optional[dict] = None,
+                 routing: str = "softmax_top", groups: Optional[tuple] = None, correction: bool = False,
+                 activation: Optional[str] = None, out_dtype: Optional[str] = None):
         super().__init__()
         if not 1 <= top <= num_experts:
             raise ValueError(f"{top} of {num_experts} experts cannot be chosen")
+        if routing not in ("softmax_top", "sigmoid_groups"):
+            raise ValueError(f"routing must be 'softmax_top' or 'sigmoid_groups', got {routing!r}")
+        if activation is not None and activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        count, keep = (int(groups[0]), int(groups[1])) if groups else (1, 1)
+        if routing == "sigmoid_groups" and (count < 1 or num_experts % count or not 1 <= keep <= count
+                                            or keep * (num_experts // count) < top):
+            raise ValueError(f"{keep} of {count} groups over {num_experts} experts cannot give {top} choices")
+        if routing == "softmax_top" and (groups or correction):
+            raise ValueError("groups and a correction go with routing 'sigmoid_groups'")
+        self.routing, self.groups, self.has_correction, self.activation = routing, (count, keep), correction, activation
+        self.out_dtype = getattr(torch, out_dtype) if out_dtype else None    # what the weighted sum is written as (None: the working dtype)
         self.hidden_size, self.num_experts, self.top, self.expert_size = hidden_size, num_experts, top, expert_size
         self.limit = float(limit) if limit is not None else 0.0
         self.alpha = float(alpha)
         self.shift = float(shift)
-        self.has_router_bias = router_bias
+        self.has_router_bias = router_bias and routing == "softmax_top"
         self.router = Linear(hidden_size, [("router", num_experts)], name="router")
         self.shared = ClampedGLU(hidden_size, **shared) if shared else None
         self._gate_up = self._down = None
@@ -83,12 +103,18 @@ class RoutedExperts(FeedForward):
     def param_decls(self):
         E, F, W = self.num_experts, self.expert_size, self.hidden_size
         gate_up, down = [], []
+        rows = F if self.activation else 2 * F          # an expert's rows in the first packed matrix: up, or gate then up
         for e in range(E):
-            gate_up += [DiskSource(f"e{e}.gate", 2 * F * e, F), DiskSource(f"e{e}.up", 2 * F * e + F, F)]
+            if self.activation:
+                gate_up.append(DiskSource(f"e{e}.up", F * e, F))
+            else:
+                gate_up += [DiskSource(f"e{e}.gate", 2 * F * e, F), DiskSource(f"e{e}.up", 2 * F * e + F, F)]
             down.append(DiskSource(f"e{e}.down", W * e, W))
-        decls = [ParamDecl("experts_gate_up", (E * 2 * F, W), sources=gate_up), ParamDecl("experts_down", (E * W, F), sources=down)]
+        decls = [ParamDecl("experts_gate_up", (E * rows, W), sources=gate_up), ParamDecl("experts_down", (E * W, F), sources=down)]
         if self.has_router_bias:
             decls.append(ParamDecl("router.b", (E,), role="vector"))
+        if self.has_correction:
+            decls.append(ParamDecl("correction", (E,), role="vector"))
         return decls
 
     def first_weight(self):
@@ -96,7 +122,7 @@ class RoutedExperts(FeedForward):
 
     def finalize(self, dtype, device):
         E, F, W = self.num_experts, self.expert_size, self.hidden_size
-        self._gate_up = self.p("experts_gate_up").view(E, 2 * F, W)
+        self._gate_up = self.p("experts_gate_up").view(E, F if self.activation else 2 * F, W)
         self._down = self.p("experts_down").view(E, W, F)
 
     def forward(self, x, ctx):
@@ -109,13 +135,21 @@ class RoutedExperts(FeedForward):
         offsets = ctx.buffer("moe_offsets", (E + 1,), torch.int32)
         order = ctx.buffer("moe_order", (T * top,), torch.int32)
         place = ctx.buffer("moe_place", (T * top,), torch.int32)
-        ops.moe_route_sort(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt, counts, offsets, order, place)
+        if self.routing == "sigmoid_groups":
+            ops.moe_route_grouped(z, self.p("correction") if self.has_correction else None, top, *self.groups, idx, wgt)
+            ops.moe_sort(idx, E, counts, offsets, order, place)
+        else:
+            ops.moe_route_sort(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt, counts, offsets, order, place)
         act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)
-        ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha, self.shift), workspace=ctx.buffer, err=ctx.error_flag)
+        if self.activation:
+            ops.moe_gemm(x, order, top, self._gate_up, offsets, act, activation=self.activation, workspace=ctx.buffer, err=ctx.error_flag)
+        else:
+            ops.moe_gemm(x, order, top, self._gate_up, offsets, act, glu=(self.limit, self.alpha, self.shift), workspace=ctx.buffer,
+                         err=ctx.error_flag)
         rows = ctx.buffer("moe_rows", (T * top, W), torch.float32)
         ops.moe_gemm(act, None, top, self._down, offsets, rows, workspace=ctx.buffer, err=ctx.error_flag)
         shared = self.shared.forward(x, ctx, out_name="moe_shared") if self.shared is not None else None
-        out = ctx.buffer("ffn_out", (T, W), ctx.act_dtype)
+        out = ctx.buffer("ffn_out", (T, W), self.out_dtype or ctx.act_dtype)
         ops.moe_combine(rows, place, wgt, shared, out)
         return out
 

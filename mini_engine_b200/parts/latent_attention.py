@@ -5,7 +5,7 @@ q = W_q h, head by head [unrotated | rotated]; W_dkv h gives kv_rank + rot_dim v
 divided by their root mean square and multiplied by a weight (the latent c), the rest one rotated key part shared by
 all heads; a head's unrotated key is W_uk c and its value W_uv c, so only c and the rotated key part are cached (one
 cache row of kv_rank + rot_dim values per token).  score = (q_unrotated . k_unrotated + q_rotated . k_rotated) * scale,
-causal.  Optional: a sink (a learned logit per head that joins the softmax's denominator once, with no key and no
+causal; with a ``window`` w a query at position p sees the keys p - w < j <= p only, and the cache keeps no more.  Optional: a sink (a learned logit per head that joins the softmax's denominator once, with no key and no
 value) and a gate (head h's output times sigmoid(W_g h)_h).
 
 The key up-projection is folded into the query (qa_h = W_uk,h^T q_h) and the value up-projection is applied to the
@@ -28,13 +28,18 @@ class LatentAttention(Mixer):
     capturable = True
 
     def __init__(self, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, scale: float,
-                 norm_eps: float, position_encoding: Optional[PartSpec | object], sink: bool = True, gate: bool = True):
+                 norm_eps: float, position_encoding: Optional[PartSpec | object], sink: bool = True, gate: bool = True,
+                 window: Optional[int] = None, out_dtype: Optional[str] = None):
         super().__init__()
         self.hidden_size, self.num_heads = hidden_size, num_heads
         self.dim, self.rot_dim, self.vdim, self.kv_rank = dim, rot_dim, vdim, kv_rank
         self.scale = float(scale)
         self.norm_eps = float(norm_eps)
         self.has_sink, self.has_gate = sink, gate
+        if window is not None and window < 1:
+            raise ValueError(f"LatentAttention: a window of {window} tokens cannot be")
+        self.window = int(window) if window else None
+        self.out_dtype = getattr(torch, out_dtype) if out_dtype else None     # what the output projection returns (None: the working dtype)
         if isinstance(position_encoding, PartSpec):
             position_encoding = build_part("position_encoding", position_encoding)
         self.rope = position_encoding
@@ -63,7 +68,7 @@ class LatentAttention(Mixer):
         return decls
 
     def cache_needs(self):
-        return [KVCacheNeed(1, self.kv_rank + self.rot_dim, None, planes=1)]
+        return [KVCacheNeed(1, self.kv_rank + self.rot_dim, self.window, planes=1)]
 
     def first_weight(self):
         return self.in_proj.weight
@@ -90,12 +95,12 @@ class LatentAttention(Mixer):
         ops.batched_heads_mm(q_plain.transpose(0, 1), self._uk, q_abs)
         o_lat = ctx.buffer("latent_o", (H, T, C), dt)
         ops.latent_attention(q_abs, q_rot, kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta,
-                             self.p("sink") if self.has_sink else None, gate, o_lat, self.scale)
+                             self.p("sink") if self.has_sink else None, gate, o_lat, self.scale, window=self.window)
         o_heads = ctx.buffer("latent_o_heads", (H, T, V), dt)
         ops.batched_heads_mm(o_lat, self._uv_t, o_heads)
         o_rows = ctx.buffer("attn_out", (T, H * V), dt)
         ops.heads_to_rows(o_heads, o_rows)
-        return self.o_proj.forward(o_rows, ctx, "mixer_out")
+        return self.o_proj.forward(o_rows, ctx, "mixer_out", out_dtype=self.out_dtype)
 
 
 register_mixer("latent_attention", LatentAttention)

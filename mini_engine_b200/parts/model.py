@@ -51,6 +51,10 @@ class ModelPlan:
                                        # indexed by token that blocks share (``SharedRef(key)`` in a ``BlockSpec``'s args)
     streams: int = 1                   # residual streams; > 1: the residual is [streams, T, hidden], all equal at the start
     logit_softcap: "Optional[float]" = None   # logits <- cap * tanh(logits / cap)
+    logit_scale: float = 1.0           # logits are multiplied by this (in front of the cap)
+    embed_norm: "Optional[PartSpec]" = None    # a norm that the embedding passes through before it becomes the residual stream
+                                       # (a norm kind with ``normalize_stream``)
+    embed_norm_prefix: str = ""
     pass_vectors: "Optional[tuple[str, int]]" = None   # (tensor name, rows): vectors of ``hidden_size`` values of which a
                                        # ``LayerCall.add_row`` names one (what each pass over looped layers adds to the stream)
 
@@ -80,6 +84,9 @@ class DecoderModel(Part):
         self.shared = {k: build_part("position_encoding", s) for k, s in plan.shared.items()}
         self.embed = TokenEmbedding(plan.vocab_size, plan.hidden_size, scale=plan.embedding_scale, streams=plan.streams,
                                     param=plan.embed_param)
+        self.embed_norm = build_part("norm", plan.embed_norm) if plan.embed_norm is not None else None
+        if self.embed_norm is not None and not hasattr(self.embed_norm, "normalize_stream"):
+            raise ValueError(f"norm kind {plan.embed_norm.kind!r} cannot normalise the stream in place (ModelPlan.embed_norm)")
         self.tables = {k: TokenEmbedding(rows, cols, param=name) for k, (name, rows, cols) in plan.tables.items()}
         self.shared.update(self.tables)
         self.pass_vectors = None
@@ -88,7 +95,8 @@ class DecoderModel(Part):
         self.blocks = [build_block(s, self.shared) for s in plan.blocks]
         self.final_norm = build_part("norm", plan.final_norm)
         tied = plan.embed_prefix + plan.embed_param if plan.tie_word_embeddings else None
-        self.head = LMHead(plan.vocab_size, plan.hidden_size, tied, param=plan.head_param, softcap=plan.logit_softcap)
+        self.head = LMHead(plan.vocab_size, plan.hidden_size, tied, param=plan.head_param, softcap=plan.logit_softcap,
+                           scale=plan.logit_scale)
         self.schedule = list(plan.schedule)
         n_slots = 1 + max((c.cache_slot for c in self.schedule), default=-1)
         # What each cache slot must hold, taken from the first call that uses it.
@@ -118,6 +126,8 @@ class DecoderModel(Part):
     # ---- structure -----------------------------------------------------------------
     def sub_parts(self):
         parts = [(self.plan.embed_prefix, self.embed)]
+        if self.embed_norm is not None:
+            parts.append((self.plan.embed_norm_prefix, self.embed_norm))
         parts += [("", t) for t in self.tables.values()]
         if self.pass_vectors is not None:
             parts.append(("", self.pass_vectors))
@@ -149,7 +159,7 @@ class DecoderModel(Part):
         ctx.token_ids = token_ids
         ctx.forward_serial = getattr(ctx, "forward_serial", 0) + 1      # what parts cache for ONE pass over the layers is keyed by this
         residual = self.embed.forward(token_ids, ctx)
-        delta = None
+        delta = self.embed_norm.normalize_stream(residual, ctx) if self.embed_norm is not None else None
         for i, call in enumerate(self.schedule):
             # the block learns what runs after it, so that its last kernel can prepare for it
             after = self.blocks[self.schedule[i + 1].block].upcoming() if i + 1 < len(self.schedule) else None

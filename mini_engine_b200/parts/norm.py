@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import AddedToResidual, Norm, NormedUpdate, ParamDecl, PendingNorm, PendingSum, StreamUpdate
+from .base import AddedToResidual, Norm, NormedUpdate, ParamDecl, PendingNorm, PendingSum, StreamCopy, StreamUpdate
 from .registry import register_norm
 
 
@@ -139,5 +139,53 @@ class LayerNorm(Norm):
         return out
 
 
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: a row is cut into ``groups`` equal consecutive parts, each part is divided by its own
+    sqrt(mean(part^2) + eps), and the whole row is multiplied by a weight (``param`` names it on disk).  One group is the
+    plain RMS norm.  Beside the usual ``forward`` (the model's last norm: nothing may be pending but a ``StreamCopy``) it has
+    the two forms that a block with its norms BEHIND the sub-layers needs: ``add_normed`` (x <- x + norm(y)) and
+    ``normalize_stream`` (x <- norm(x), the norm behind an embedding).  Both return the new stream in the working dtype as a
+    ``StreamCopy``; in the float32 engine that is the stream itself."""
+    capturable = True
+
+    def __init__(self, size: int, eps: float, groups: int = 1, param: str = "weight"):
+        super().__init__()
+        if groups < 1 or size % groups:
+            raise ValueError(f"GroupRMSNorm: {size} values do not split into {groups} equal groups")
+        self.size, self.eps, self.groups, self.param = size, float(eps), int(groups), param
+
+    def param_decls(self):
+        return [ParamDecl(self.param, (self.size,), init="norm", role="vector")]
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return self.p(self.param)
+
+    def _copy(self, residual, ctx):
+        return None if ctx.act_dtype == torch.float32 else ctx.buffer("stream_copy", tuple(residual.shape), ctx.act_dtype)
+
+    def add_normed(self, residual, y, ctx) -> StreamCopy:
+        """``residual += norm(y)``; ``y`` [T, size] in any dtype the kernels know."""
+        out = self._copy(residual, ctx)
+        ops.group_norm(residual, y, self.weight, self.groups, self.eps, out)
+        return StreamCopy(residual if out is None else out)
+
+    def normalize_stream(self, residual, ctx) -> StreamCopy:
+        out = self._copy(residual, ctx)
+        ops.group_norm(residual, None, self.weight, self.groups, self.eps, out)
+        return StreamCopy(residual if out is None else out)
+
+    def forward(self, residual, delta, ctx, rows: Optional[torch.Tensor] = None, lazy: bool = False):
+        if delta is not None and not isinstance(delta, (StreamCopy, AddedToResidual)):
+            raise TypeError(f"GroupRMSNorm reads a stream that holds every sum; a pending {type(delta).__name__} cannot join it here")
+        if rows is None:
+            rows = ctx.buffer("all_rows", (residual.shape[0],), torch.int32)
+            torch.arange(residual.shape[0], dtype=torch.int32, device=residual.device, out=rows)
+        out = ctx.buffer("norm_out", (rows.shape[0], self.size), ctx.act_dtype)
+        ops.group_norm(residual, None, self.weight, self.groups, self.eps, out, rows=rows)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("group_rmsnorm", GroupRMSNorm)
 register_norm("layernorm", LayerNorm)
