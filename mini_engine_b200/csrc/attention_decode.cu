@@ -452,6 +452,10 @@ struct DecodePrep {
   int keep_first;             // a window also shows the keys j < keep_first
   int chunk;                  // instead of a window: the keys of the query's own chunk, from floor(p / chunk) * chunk on
   float softcap;              // c > 0: scores become c tanh(score * scale / c)
+  // the cache is one of pooled blocks (one row per block of pool_p tokens): the request sees its first
+  // max(0, context - pool_window) / pool_p rows, all of them, and nothing of this step is among them (0: an ordinary cache)
+  int pool_p;
+  int pool_window;
 };
 
 // The two products are mma.sync m16n8k16 with ldmatrix.
@@ -481,7 +485,7 @@ decode_partition_tma_mma_kernel(const __grid_constant__ CUtensorMap kv_map, cons
   const int G = nh / nkv, head_tiles = (G + 15) / 16;
   const int b = blockIdx.x, kvh = blockIdx.y / head_tiles, g0 = (blockIdx.y % head_tiles) * 16;
   const int z = blockIdx.z;
-  const int L = context_lens[b];
+  const int L = prep.pool_p > 0 ? max(0, context_lens[b] - prep.pool_window) / prep.pool_p : context_lens[b];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, t4 = lane & 3;
   const int n_g = min(16, G - g0);
   // The page of this lane's piece of the partition is asked for together with the context length (which page it
@@ -823,7 +827,7 @@ template <int HD, bool FUSED, int VBUF, int QROWS, bool TILED = false>
 static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_parts, cudaStream_t stream, const void* qkv,
                                     int64_t q_row_stride, const int* bt, int bt_stride, const int* cu, const int* cl, int nh,
                                     int nkv, int page_size, float scale, int window, float* to, float* tm, float* tl, int tiles,
-                                    int* err, const DecodePrep& prep) {
+                                    int* err, const DecodePrep& prep, int grid_parts = 0) {
   const size_t smem = (size_t)(QROWS + DEC_PART + VBUF * DEC_PART / 2) * HD * sizeof(bf16) + 1024;
   static bool attr_set = false;
   if (!attr_set) {
@@ -832,7 +836,7 @@ static int launch_partition_tma_mma(const void* kv_map, int num_reqs, int max_pa
     attr_set = true;
   }
   const int G = nh / nkv;
-  dim3 grid(num_reqs, nkv * ((G + 15) / 16), max_parts);
+  dim3 grid(num_reqs, nkv * ((G + 15) / 16), grid_parts > 0 ? grid_parts : max_parts);     // (max_parts: the stride of a head's slots)
   me_launch(decode_partition_tma_mma_kernel<HD, FUSED, VBUF, QROWS, TILED>, grid, dim3(DEC_THREADS), smem, stream,
       *reinterpret_cast<const CUtensorMap*>(kv_map), (const bf16*)qkv, q_row_stride, bt, bt_stride, cu, cl, nh, nkv, page_size,
       scale, window, to, tm, tl, max_parts, tiles, err, prep);
@@ -849,7 +853,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
                                     const float* __restrict__ tmp_out, const float* __restrict__ tmp_m,
                                     const float* __restrict__ tmp_l, int nh, int hd, int max_parts, int part_keys,
                                     int sink, const float* __restrict__ gate, int64_t gate_stride,
-                                    const float* __restrict__ sinks) {
+                                    const float* __restrict__ sinks, int pool_base, int pool_parts, int pool_p, int pool_window) {
   constexpr int CHUNK = 128;                         // partitions whose factors are held in shared memory at a time
   __shared__ float f_s[CHUNK], red[32];
   const int b = blockIdx.x, h = blockIdx.y;
@@ -859,7 +863,11 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
   const int64_t tok = cu_seqlens[b];
   pdl_wait();
   pdl_launch_dependents();
-  const int P = max(1, min(max_parts, (L + part_keys - 1) / part_keys));
+  // With pooled blocks a head's slots hold two runs of partitions: those over the tokens from slot 0 on, and those over the
+  // request's pooled blocks from slot pool_base on.
+  const int P_tok = max(1, min(pool_p > 0 ? pool_base : max_parts, (L + part_keys - 1) / part_keys));
+  const int P = P_tok + (pool_p > 0 ? min(pool_parts, (max(0, L - pool_window) / pool_p + part_keys - 1) / part_keys) : 0);
+  auto slot = [&](int p) { return p < P_tok ? p : pool_base + (p - P_tok); };
   const int64_t row0 = ((int64_t)b * nh + h) * max_parts;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
   if (P <= 16 && hd <= (int)blockDim.x) {
@@ -868,9 +876,9 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
     float mv[16], lv[16], ov[16];
 #pragma unroll
     for (int p = 0; p < 16; ++p) {
-      mv[p] = p < P ? tmp_m[row0 + p] : -INFINITY;
-      lv[p] = p < P ? tmp_l[row0 + p] : 0.f;
-      ov[p] = (p < P && tid < hd) ? tmp_out[(row0 + p) * hd + tid] : 0.f;     // (never written where mv is -inf: not used then)
+      mv[p] = p < P ? tmp_m[row0 + slot(p)] : -INFINITY;
+      lv[p] = p < P ? tmp_l[row0 + slot(p)] : 0.f;
+      ov[p] = (p < P && tid < hd) ? tmp_out[(row0 + slot(p)) * hd + tid] : 0.f;     // (never written where mv is -inf: not used then)
     }
     float M = sink ? sink_score : -INFINITY;         // the sink: a key of score 0 (or a learned one) that has no value
 #pragma unroll
@@ -892,7 +900,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
   }
   // the largest maximum: a partition per thread, then lanes, then warps
   float mx = -INFINITY;
-  for (int p = tid; p < P; p += blockDim.x) mx = fmaxf(mx, tmp_m[row0 + p]);
+  for (int p = tid; p < P; p += blockDim.x) mx = fmaxf(mx, tmp_m[row0 + slot(p)]);
   mx = warp_max(mx);
   if (lane == 0) red[warp] = mx;
   __syncthreads();
@@ -903,7 +911,7 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
     const int n = min(CHUNK, P - p0);
     __syncthreads();
     for (int p = tid; p < n; p += blockDim.x) {
-      const float mp = tmp_m[row0 + p0 + p];
+      const float mp = tmp_m[row0 + slot(p0 + p)];
       f_s[p] = mp == -INFINITY ? 0.f : expf(mp - M);
     }
     __syncthreads();
@@ -915,8 +923,8 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const bool ok = q0 + i < n && f_s[q0 + i] != 0.f;
-          lv[i] = ok ? tmp_l[row0 + p0 + q0 + i] : 0.f;
-          ov[i] = ok && tid < hd ? tmp_out[(row0 + p0 + q0 + i) * hd + tid] : 0.f;
+          lv[i] = ok ? tmp_l[row0 + slot(p0 + q0 + i)] : 0.f;
+          ov[i] = ok && tid < hd ? tmp_out[(row0 + slot(p0 + q0 + i)) * hd + tid] : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) {               // partitions in index order
@@ -934,11 +942,11 @@ __global__ void decode_merge_kernel(T* __restrict__ out, int64_t out_row_stride,
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const bool ok = q0 + i < n && f_s[q0 + i] != 0.f;
-        lv[i] = ok ? tmp_l[row0 + p0 + q0 + i] : 0.f;
+        lv[i] = ok ? tmp_l[row0 + slot(p0 + q0 + i)] : 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int d = tid + c * (int)blockDim.x;
-          ov[c][i] = ok && d < hd ? tmp_out[(row0 + p0 + q0 + i) * hd + d] : 0.f;
+          ov[c][i] = ok && d < hd ? tmp_out[(row0 + slot(p0 + q0 + i)) * hd + d] : 0.f;
         }
       }
 #pragma unroll
@@ -984,7 +992,8 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
                           int num_reqs, int nh, int nkv, int hd, int page_size, float scale,
                           int window, float* tmp_out, float* tmp_m, float* tmp_l, int max_parts,
                           int* err, int kind, const void* kv_map, int sink, const float* gate, int64_t gate_stride,
-                          int keep_first, int chunk, float softcap, const float* sinks, cudaStream_t stream) {
+                          int keep_first, int chunk, float softcap, const float* sinks, const void* pool_map,
+                          const int* pooled_tables, int pbt_stride, int pool_p, int pool_parts, cudaStream_t stream) {
   if (num_reqs == 0) return 0;
   ME_REQUIRE(hd % 8 == 0 && hd >= 8 && hd <= 256, "me_attn_decode: head_dim %d is not a multiple of 8 up to 256", hd);
   ME_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "me_attn_decode: %d heads, %d kv heads", nh, nkv);
@@ -1014,16 +1023,35 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
              "me_attn_decode: a window (with kept first keys) or chunks, not both");
   ME_REQUIRE(tma_mma || (keep_first == 0 && chunk == 0 && softcap == 0.f),
              "me_attn_decode: kept first keys, chunks and capped scores need the kernel fed by tensor-map loads");
+  // Pooled blocks (pool_p > 0; the tensor-map kernel's alone, with a plain window): the last pool_parts of a head's max_parts slots
+  // take the partitions of a second launch over the cache of pooled blocks, whose "context" is the number of blocks the
+  // request sees; the merge joins both runs.
+  ME_REQUIRE(pool_p == 0 || (pool_p > 0 && tma_mma && pool_map && pooled_tables && window > 0 && keep_first == 0 && chunk == 0 &&
+                             pool_parts >= 1 && pool_parts < max_parts),
+             "me_attn_decode: pooled blocks of %d tokens need the kernel fed by tensor-map loads, their cache, a plain window and slots", pool_p);
+  const int tok_parts = pool_p > 0 ? max_parts - pool_parts : max_parts;
   if (tma_mma) {
     DecodePrep none = {};
     none.keep_first = keep_first;
     none.chunk = chunk;
     none.softcap = softcap;
     int rc = hd == 64 ? launch_partition_tma_mma<64, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                            cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none)
+                                                            cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none, tok_parts)
                       : launch_partition_tma_mma<128, false, 2, 16>(kv_map, num_reqs, max_parts, stream, qkv, q_row_stride, block_tables, bt_stride,
-                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none);
+                                                             cu_seqlens, context_lens, nh, nkv, page_size, scale, window, tmp_out, tmp_m, tmp_l, 1, err, none, tok_parts);
     if (rc) return rc;
+    if (pool_p > 0) {
+      DecodePrep blocks = {};
+      blocks.softcap = softcap;
+      blocks.pool_p = pool_p;
+      blocks.pool_window = window;
+      float *to = tmp_out + (int64_t)tok_parts * hd, *tm = tmp_m + tok_parts, *tl = tmp_l + tok_parts;
+      rc = hd == 64 ? launch_partition_tma_mma<64, false, 2, 16>(pool_map, num_reqs, max_parts, stream, qkv, q_row_stride, pooled_tables, pbt_stride,
+                                                          cu_seqlens, context_lens, nh, nkv, page_size, scale, 0, to, tm, tl, 1, err, blocks, pool_parts)
+                    : launch_partition_tma_mma<128, false, 2, 16>(pool_map, num_reqs, max_parts, stream, qkv, q_row_stride, pooled_tables, pbt_stride,
+                                                           cu_seqlens, context_lens, nh, nkv, page_size, scale, 0, to, tm, tl, 1, err, blocks, pool_parts);
+      if (rc) return rc;
+    }
   }
   if (mma) {
     ME_REQUIRE((int64_t)nkv * ((G + 15) / 16) <= 65535, "me_attn_decode: too many heads");
@@ -1049,7 +1077,7 @@ ME_API int me_attn_decode(const void* qkv, int dtype, int64_t q_row_stride, void
   const int mthreads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
   ME_DISPATCH_DTYPE(dtype, T, (me_launch(decode_merge_kernel<T>, mgrid, dim3(mthreads), 0, stream,
       (T*)out, out_row_stride, cu_seqlens, context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART, sink, gate,
-      gate_stride, sinks)));
+      gate_stride, sinks, tok_parts, pool_parts, pool_p, window)));
   ME_LAUNCH_CHECK("me_attn_decode (merge)");
   return 0;
 }
@@ -1119,7 +1147,7 @@ ME_API int me_attn_decode_fused(const void* qkv, int64_t q_row_stride, void* out
   dim3 mgrid(num_reqs, nh);
   me_launch(decode_merge_kernel<bf16>, mgrid, dim3(hd >= 128 ? 128 : 64), 0, stream, (bf16*)out, out_row_stride, cu_seqlens,
             context_lens, tmp_out, tmp_m, tmp_l, nh, hd, max_parts, DEC_PART * tiles, 0, (const float*)nullptr, (int64_t)0,
-            (const float*)nullptr);
+            (const float*)nullptr, 0, 0, 0, 0);
   ME_LAUNCH_CHECK("me_attn_decode_fused (merge)");
   return 0;
 }

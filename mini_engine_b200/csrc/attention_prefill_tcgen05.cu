@@ -380,8 +380,10 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
                                        const int* __restrict__ tiles, int nh, int nkv, int gp, int page_size, float scale_log2,
                                        int window, int sink, const float* __restrict__ gate, int64_t gate_stride,
                                        int* __restrict__ err, int keep_first_arg, int chunk_arg, float softcap_arg,
-                                       const float* __restrict__ sinks_arg) {
+                                       const float* __restrict__ sinks_arg, const __grid_constant__ CUtensorMap pool_map,
+                                       const int* __restrict__ pooled_tables, int pbt_stride, int pool_p_arg) {
   const int keep_first = EXTRA ? keep_first_arg : 0, chunk = EXTRA ? chunk_arg : 0;
+  const int pool_p = EXTRA ? pool_p_arg : 0;
   const float softcap = EXTRA ? softcap_arg : 0.f;
   const float* __restrict__ sinks = EXTRA ? sinks_arg : nullptr;
   constexpr int KEYS = 128, HALVES = HD / 64;
@@ -414,8 +416,18 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
   const int lo_seen = lo;
   lo = (lo / KEYS) * KEYS;
   const int n_first = keep_first > 0 ? min((keep_first + KEYS - 1) / KEYS, lo / KEYS) : 0;
-  const int n_tiles = n_first + (hi - lo + KEYS - 1) / KEYS;
-  auto tile_start = [&](int it) { return (EXTRA && it < n_first) ? it * KEYS : lo + (it - n_first) * KEYS; };
+  // Pooled blocks (pool_p > 0, with a window): a second cache of the same layout holds one row per block of pool_p tokens;
+  // the row at position p sees the blocks b with (b + 1) pool_p <= p - window + 1.  Their tiles, counted from block 0, come
+  // before all others; a tile's "keys" are then block numbers.
+  auto blocks_seen = [&](int p) { return (pool_p > 0 && p - window + 1 > 0) ? (p - window + 1) / pool_p : 0; };
+  const int nb_lo = EXTRA ? blocks_seen(p_lo) : 0, nb_hi = EXTRA ? blocks_seen(p_hi) : 0;
+  const int n_pool = EXTRA ? (nb_hi + KEYS - 1) / KEYS : 0;
+  const int n_tiles = n_pool + n_first + (hi - lo + KEYS - 1) / KEYS;
+  auto tile_start = [&](int it) {
+    if (EXTRA && it < n_pool) return it * KEYS;
+    return (EXTRA && it - n_pool < n_first) ? (it - n_pool) * KEYS : lo + (it - n_pool - n_first) * KEYS;
+  };
+  const int* pbt = (EXTRA && pool_p > 0) ? pooled_tables + (int64_t)b * pbt_stride : nullptr;
   // With a cap c the scores become c tanh(s * scale / c) before anything else; exponents then take log2(e) alone.
   const float sl2 = softcap > 0.f ? 1.4426950408889634f : scale_log2;
   const float cap_in = softcap > 0.f ? scale_log2 * (2.0f / softcap) : 0.f;      // s -> 2 log2(e) s scale / c
@@ -437,6 +449,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     tma::mbar_fence_init();
     tma::prefetch_map(&q_map);
     tma::prefetch_map(&kv_map);
+    if (EXTRA && pool_p > 0) tma::prefetch_map(&pool_map);
   }
   if (warp == 1) tc5::tmem_alloc(&tmem_slot, TMEM_COLS);
   tc5::fence_before_sync();
@@ -448,11 +461,17 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
   const int boxes = (KEYS / page_size) * HALVES;
   const int row_off = is_v ? nkv * page_size : 0;
   const int pg = lane / HALVES, hf = lane % HALVES;
-  auto first_row_of = [&](int kt) {
+  auto first_row_of = [&](int it) {
     int first_row = -1;
+    const int kt = tile_start(it);
     if (lane < boxes) {
       const int j0 = kt + pg * page_size;
-      if (j0 < hi && (j0 + page_size > lo_seen || (EXTRA && j0 < keep_first))) {
+      if (EXTRA && it < n_pool) {
+        if (j0 < nb_hi) {
+          const int page = pbt[j0 / page_size];
+          if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size + row_off;
+        }
+      } else if (j0 < hi && (j0 + page_size > lo_seen || (EXTRA && j0 < keep_first))) {
         const int page = bt[j0 / page_size];
         if (page >= 0) first_row = ((page * 2) * nkv + kvh) * page_size + row_off;
       }
@@ -460,7 +479,7 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     return first_row;
   };
   int first_row_0 = -1;
-  if (warp == 0 || warp == 10) first_row_0 = first_row_of(tile_start(0));
+  if (warp == 0 || warp == 10) first_row_0 = first_row_of(0);
   pdl_wait();
   bool ok = true;
 
@@ -479,16 +498,17 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     unsigned long long* const full = is_v ? v_full : k_full;
     unsigned long long* const empty = is_v ? v_empty : k_empty;
     for (int it = 0; it < n_tiles && ok; ++it) {
-      const int s = it % RING, kt = tile_start(it);
+      const int s = it % RING;
       ok = tma::mbar_wait(&empty[s], ((it / RING) & 1) ^ 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      const int first_row = it == 0 ? first_row_0 : first_row_of(kt);
+      const int first_row = it == 0 ? first_row_0 : first_row_of(it);
       const unsigned n_boxes = __popc(__ballot_sync(0xffffffffu, first_row >= 0));
       if (lane == 0) tma::mbar_expect_tx(&full[s], n_boxes * box_bytes);
       __syncwarp();
       if (first_row >= 0)
-        tma::load_2d(dst0 + s * KV_BYTES + hf * KB_BYTES + pg * page_size * 128, &kv_map, hf * 64, first_row, &full[s]);
+        tma::load_2d(dst0 + s * KV_BYTES + hf * KB_BYTES + pg * page_size * 128, (EXTRA && it < n_pool) ? &pool_map : &kv_map, hf * 64,
+                     first_row, &full[s]);
     }
   } else if (warp == 1) {
     // The issuing warp: all lanes run the loop with the same values, an elected lane issues.
@@ -548,17 +568,22 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
     const int j_max = row_ok ? pos : -(1 << 30);
     const int j_min = window > 0 ? pos - window + 1 : (chunk > 0 ? (pos / chunk) * chunk : -(1 << 30));
     const int chunk_hi = chunk > 0 ? (p_hi / chunk) * chunk : 0;
+    const int nb_row = (EXTRA && row_ok) ? blocks_seen(pos) : 0;     // the pooled blocks this row sees: [0, nb_row)
     // Both groups run every named barrier of every tile, also after a wait has given up (ok == false): then only
     // the work is skipped, so no warp is left waiting for a partner that has gone.
     for (int it = g; it < n_tiles; it += 2) {
       const int kt = tile_start(it);
       const uint32_t t_s = tmem_s + (it % 3) * KEYS + t_row;
-      const bool need_mask = kt + KEYS - 1 > p_lo || (window > 0 && kt <= p_hi - window) || (EXTRA && kt < chunk_hi) || n_tok * gp < TA_ROWS;
+      const bool of_blocks = EXTRA && it < n_pool;         // the tile's columns are pooled blocks kt .. kt + KEYS - 1
+      const bool need_mask = of_blocks ? (kt + KEYS > nb_lo || n_tok * gp < TA_ROWS)
+                                       : (kt + KEYS - 1 > p_lo || (window > 0 && kt <= p_hi - window) || (EXTRA && kt < chunk_hi) || n_tok * gp < TA_ROWS);
       // Q K^T (it) was issued after Q K^T (it - 3), which this group's last tile (it - 2) waited for in its turn.
       if (ok) ok = tma::mbar_wait(&s_ready[it % 3], (it / 3) & 1);
       ok = __all_sync(0xffffffffu, ok);
       float mx = neg_inf;
-      const int c_min = j_min - kt, c_max = j_max - kt, c_keep = keep_first - kt;      // the same as columns of this tile
+      // the same as columns of this tile (a row sees the blocks below nb_row and no others)
+      const int c_min = of_blocks ? -(1 << 30) : j_min - kt, c_max = of_blocks ? nb_row - 1 - kt : j_max - kt;
+      const int c_keep = of_blocks ? -(1 << 30) : keep_first - kt;
       auto seen = [&](int col) { return col <= c_max && (col >= c_min || (EXTRA && col < c_keep)); };
       // A masked tile by pieces of 32 columns: the rows of a warp are consecutive tokens (of one or two heads), so
       // most pieces are seen whole, or not at all, by the whole warp; only the others are tested column by column.
@@ -638,12 +663,13 @@ attn_prefill_tcgen05_two_groups_kernel(const __grid_constant__ CUtensorMap q_map
           }
         }
       }
-      if (kt + KEYS > hi || kt < lo_seen) {
+      const int t_hi = of_blocks ? nb_hi : hi, t_lo = of_blocks ? 0 : lo_seen;       // the tile's rows of V that may be used
+      if (kt + KEYS > t_hi || kt < t_lo) {
         // Rows of V that hold no key this tile may use must be zero (0 * anything-else would not be 0).  The load
         // before this one into the buffer, V (it - 3), is over: P V (it - 3) was issued before Q K^T (it).
         if (ok) ok = tma::mbar_wait(&v_full[it % RING], (it / RING) & 1);
         const int j = kt + r;
-        if (ok && (j >= hi || (j < lo_seen && (!EXTRA || j >= keep_first)))) {
+        if (ok && (j >= t_hi || (j < t_lo && (!EXTRA || j >= keep_first)))) {
 #pragma unroll
           for (int hf = 0; hf < HALVES; ++hf) {
             uint4* row = reinterpret_cast<uint4*>(v_s + (it % RING) * KV_BYTES + hf * KB_BYTES + r * 128);
@@ -765,7 +791,8 @@ template <int HD, int KT, bool TWO_GROUPS>
 int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride, const int* block_tables, int bt_stride,
               const int* cu_seqlens, const int* context_lens, const int* tiles, int num_tiles, int nh, int nkv, int gp,
               int page_size, float scale, int window, int sink, const float* gate, int64_t gate_stride, int* err,
-              int keep_first, int chunk, float softcap, const float* sinks, cudaStream_t stream) {
+              int keep_first, int chunk, float softcap, const float* sinks, const void* pool_map, const int* pooled_tables,
+              int pbt_stride, int pool_p, cudaStream_t stream) {
   const size_t smem = TWO_GROUPS ? (size_t)TA_ROWS * HD * 2 + 6 * (size_t)KT * HD * 2 + 1024
                                  : (size_t)TA_ROWS * HD * 2 + 4 * (size_t)KT * HD * 2 + 2 * (size_t)TA_ROWS * KT * 2 + 1024;
   static bool attr_set = false;
@@ -782,12 +809,13 @@ int launch_ta(const void* q_map, const void* kv_map, void* out, int64_t out_row_
   // and 16% slower at 2,048, where the last round then holds long tiles.)
   dim3 grid(nkv * (nh / nkv / gp), num_tiles);
   if constexpr (TWO_GROUPS) {
-    auto kernel = (keep_first > 0 || chunk > 0 || softcap > 0.f || sinks) ? attn_prefill_tcgen05_two_groups_kernel<HD, true>
+    auto kernel = (keep_first > 0 || chunk > 0 || softcap > 0.f || sinks || pool_p > 0) ? attn_prefill_tcgen05_two_groups_kernel<HD, true>
                                                                           : attn_prefill_tcgen05_two_groups_kernel<HD, false>;
     me_launch(kernel, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
               *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
               context_lens, tiles, nh, nkv, gp, page_size, scale * 1.4426950408889634f, window, sink, gate, gate_stride, err,
-              keep_first, chunk, softcap, sinks);
+              keep_first, chunk, softcap, sinks, *reinterpret_cast<const CUtensorMap*>(pool_p > 0 ? pool_map : kv_map), pooled_tables,
+              pbt_stride, pool_p);
   } else
     me_launch(attn_prefill_tcgen05_kernel<HD, KT>, grid, dim3(TA_THREADS), smem, stream, *reinterpret_cast<const CUtensorMap*>(q_map),
               *reinterpret_cast<const CUtensorMap*>(kv_map), (bf16*)out, out_row_stride, block_tables, bt_stride, cu_seqlens,
@@ -814,12 +842,15 @@ ME_API int me_attn_prefill_tcgen05_heads_per_block(int nh, int nkv, int hd, int 
 // nh * head_dim pre-activations (or null): the output is multiplied by their sigmoid.  ``keep_first``: the window also shows
 // keys j < keep_first.  ``chunk`` (instead of a window): a query at p sees the keys j <= p from floor(p / chunk) * chunk on.
 // ``softcap`` c: scores become c tanh(score * scale / c).  ``sinks``: float32 [nh], the extra term is exp(sinks[head]),
-// neither scaled nor capped.  These four are the kernel with two groups' alone.
+// neither scaled nor capped.  ``pool_map``, ``pooled_tables``, ``pool_p``: a second cache of the same layout with one row per
+// block of pool_p tokens and its block tables; with a window a query at p also sees the blocks b with (b + 1) pool_p <=
+// p - window + 1 (0: none).  These five are the kernel with two groups' alone.
 ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* out, int64_t out_row_stride,
                                    const int* block_tables, int bt_stride, const int* cu_seqlens, const int* context_lens,
                                    const int* tiles, int num_tiles, int nh, int nkv, int hd, int page_size, float scale,
                                    int window, int key_tile, int sink, const float* gate, int64_t gate_stride, int* err,
-                                   int keep_first, int chunk, float softcap, const float* sinks, cudaStream_t stream) {
+                                   int keep_first, int chunk, float softcap, const float* sinks, const void* pool_map,
+                                   const int* pooled_tables, int pbt_stride, int pool_p, cudaStream_t stream) {
   if (num_tiles == 0) return 0;
   const int gp = me_attn_prefill_tcgen05_heads_per_block(nh, nkv, hd, page_size);
   ME_REQUIRE(gp > 0, "me_attn_prefill_tcgen05: head_dim %d, %d/%d heads, pages of %d are not taken", hd, nh, nkv, page_size);
@@ -829,15 +860,18 @@ ME_API int me_attn_prefill_tcgen05(const void* q_map, const void* kv_map, void* 
   // key_tile: keys per step of the loop.  128 (and 0): the kernel with two softmax groups and P in tensor memory, the
   // faster one; 64: the kernel with one group and P in shared memory, which needs less of both memories.
   if (key_tile == 0) key_tile = 128;
-  ME_REQUIRE(key_tile == 128 || (keep_first == 0 && chunk == 0 && softcap == 0.f && sinks == nullptr),
-             "me_attn_prefill_tcgen05: kept first keys, chunks, capped scores and learned sinks need the key tile of 128");
+  ME_REQUIRE(key_tile == 128 || (keep_first == 0 && chunk == 0 && softcap == 0.f && sinks == nullptr && pool_p == 0),
+             "me_attn_prefill_tcgen05: kept first keys, chunks, capped scores, learned sinks and pooled blocks need the key tile of 128");
+  ME_REQUIRE(pool_p == 0 || (pool_p > 0 && pool_map && pooled_tables && window > 0 && keep_first == 0 && chunk == 0),
+             "me_attn_prefill_tcgen05: pooled blocks of %d tokens need their cache and a plain window", pool_p);
   ME_REQUIRE(keep_first >= 0 && chunk >= 0 && softcap >= 0.f && !(chunk > 0 && window > 0) && (keep_first == 0 || window > 0),
              "me_attn_prefill_tcgen05: a window (with kept first keys) or chunks, not both");
   ME_REQUIRE((key_tile == 64 || key_tile == 128) && key_tile % page_size == 0, "me_attn_prefill_tcgen05: key tile %d with pages of %d",
              key_tile, page_size);
   int rc;
 #define ME_TA_ARGS q_map, kv_map, out, out_row_stride, block_tables, bt_stride, cu_seqlens, context_lens, tiles, num_tiles, nh, nkv, gp, \
-                   page_size, scale, window, sink, gate, gate_stride, err, keep_first, chunk, softcap, sinks, stream
+                   page_size, scale, window, sink, gate, gate_stride, err, keep_first, chunk, softcap, sinks, pool_map, pooled_tables, \
+                   pbt_stride, pool_p, stream
   if (hd == 64) rc = key_tile == 64 ? launch_ta<64, 64, false>(ME_TA_ARGS) : launch_ta<64, 128, true>(ME_TA_ARGS);
   else rc = key_tile == 64 ? launch_ta<128, 64, false>(ME_TA_ARGS) : launch_ta<128, 128, true>(ME_TA_ARGS);
 #undef ME_TA_ARGS

@@ -39,7 +39,7 @@ _PROTOS = {
     "me_gemm_simt": [_P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _P],
     "me_qk_norm_rope_kv_write": [_P, _I, _L, _I, _I, _I, _I, _P, _P, _F, _P, _I, _P, _P, _P, _I, _P],
     "me_attn_chunk": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
-    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _I, _P, _L, _I, _I, _F, _P, _P],
+    "me_attn_decode": [_P, _I, _L, _P, _L, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _P, _I, _P, _I, _P, _I, _P, _L, _I, _I, _F, _P, _P, _P, _I, _I, _I, _P],
     "me_attn_decode_fused": [_P, _L, _P, _L, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P, _P, _F, _P, _P, _P, _P, _P,
                              _I, _I, _I, _P, _P],
     "me_gemm_decode": [_I, _P, _L, _P, _I, _F, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _P, ctypes.c_uint64, _F, _F, _F, _P],
@@ -47,7 +47,7 @@ _PROTOS = {
     "me_gemm_tcgen05": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _L, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_persistent": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
     "me_gemm_tcgen05_shared": [_P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P],
-    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _L, _P, _I, _I, _F, _P, _P],
+    "me_attn_prefill_tcgen05": [_P, _P, _P, _L, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P, _L, _P, _I, _I, _F, _P, _P, _P, _I, _I, _P],
     "me_tma_encode_2d": [_P, _P, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint32, _I],
     "me_attn_prefill": [_P, _L, _P, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     "me_sample": [_P, _L, _P, _P, _P, _P, _I, _I, _P, _P, _P],
@@ -848,13 +848,14 @@ def prefill_tcgen05_heads_per_block(num_heads: int, num_kv_heads: int, head_dim:
 def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
                               scale, window, tiles=None, num_tiles=None, key_tile: int = 0, sink: bool = False,
                               gate: Optional[torch.Tensor] = None, keep_first: int = 0, chunk: int = 0, softcap: float = 0.0,
-                              sinks: Optional[torch.Tensor] = None) -> None:
+                              sinks: Optional[torch.Tensor] = None, pooled: Optional[tuple] = None) -> None:
     """The tcgen05 / tensor-memory prefill kernel (bfloat16, head_dim 64 or 128, page sizes dividing 128) over
     tiles of 128 / heads-per-block tokens; Q, K and V arrive by tensor-map loads.  ``sink``: one more term, exp(0), in
     the softmax's denominator; ``gate``: float32 rows of pre-activations whose sigmoid multiplies the output.
     ``keep_first``: the window also shows the keys j < keep_first; ``chunk`` (instead of a window): the keys of the query's
     own chunk; ``softcap`` c: scores become c tanh(s / c) after the scale; ``sinks`` (float32 [heads]): the extra term is
-    exp(sinks[head]) (the kernel with the key tile of 128 only)."""
+    exp(sinks[head]); ``pooled`` = (cache, block tables, P): the blocks of P tokens in front of the window, one row each in a
+    second cache of the same layout (the kernel with the key tile of 128 only)."""
     gp = prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, head_dim, page_size)
     _need(gp > 0 and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.data_ptr() % 16 == 0,
           "attention_prefill_tcgen05: shape or dtype not taken by the kernel")
@@ -865,7 +866,9 @@ def attention_prefill_tcgen05(qkv, out, num_heads, num_kv_heads, head_dim, pool,
           out.stride(0), block_tables.data_ptr(), block_tables.stride(0), meta.cu_seqlens.data_ptr(),
           meta.context_lens.data_ptr(), tiles.data_ptr(), num_tiles, num_heads, num_kv_heads, head_dim, page_size,
           float(scale), int(window or 0), key_tile, 1 if sink else 0, _ptr(gate), gate.stride(0) if gate is not None else 0,
-          meta.error_flag.data_ptr(), int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), _ptr(sinks), _stream())
+          meta.error_flag.data_ptr(), int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), _ptr(sinks),
+          kv_tensor_map(pooled[0], page_size).ptr if pooled else 0, pooled[1].data_ptr() if pooled else 0,
+          pooled[1].stride(0) if pooled else 0, int(pooled[2]) if pooled else 0, _stream())
 
 
 use_tcgen05_attention = True   # False: portions of prompts use the mma.sync kernel instead (a switch for comparisons)
@@ -873,7 +876,8 @@ use_tcgen05_attention = True   # False: portions of prompts use the mma.sync ker
 
 def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_size, block_tables, meta,
                      scale, window, kind: str = "auto", sink: bool = False, gate: Optional[torch.Tensor] = None,
-                     keep_first: int = 0, chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None) -> None:
+                     keep_first: int = 0, chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                     pooled: Optional[tuple] = None) -> None:
     """The split-K decode kernel and its merge over requests [0, meta.num_decodes).  ``sink``: one more term, exp(0), in
     the softmax's denominator (added once, in the merge); ``gate``: float32 rows of pre-activations whose sigmoid
     multiplies the output.  ``sinks`` (float32 [heads]): the term is exp(sinks[head]).  ``keep_first``, ``chunk`` and
@@ -885,6 +889,12 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
     D = meta.num_decodes
     parts = max(1, (meta.max_context_len + DECODE_PARTITION - 1) // DECODE_PARTITION)
     room = max(parts, (getattr(meta, "scratch_context_len", 0) + DECODE_PARTITION - 1) // DECODE_PARTITION)
+    pool_parts = 0
+    if pooled is not None:
+        # ``pooled`` = (cache, block tables, P): a second launch over the cache of pooled blocks fills the last slots of a head
+        rows = lambda n: ((n + int(pooled[2]) - 1) // int(pooled[2]) + DECODE_PARTITION - 1) // DECODE_PARTITION
+        pool_parts = max(1, rows(meta.max_context_len))
+        parts, room = parts + pool_parts, room + max(pool_parts, rows(getattr(meta, "scratch_context_len", 0)))
     tmp_out = meta.workspace("decode_tmp_out", (D * num_heads * room * head_dim,), torch.float32)
     tmp_ml = meta.workspace("decode_tmp_ml", (2, D * num_heads * room), torch.float32)
     tm = kv_tensor_map(pool, page_size) if kind in ("auto", "tensor_cores_tma") else None
@@ -894,9 +904,10 @@ def attention_decode(qkv, out, num_heads, num_kv_heads, head_dim, pool, page_siz
           int(window or 0), tmp_out.data_ptr(), tmp_ml[0].data_ptr(), tmp_ml[1].data_ptr(), parts,
           _ptr(meta.error_flag), DECODE_KINDS[kind], tm.ptr if tm is not None else 0, 1 if sink else 0, _ptr(gate),
           gate.stride(0) if gate is not None else 0, int(keep_first or 0), int(chunk or 0), float(softcap or 0.0), _ptr(sinks),
-          _stream())
+          kv_tensor_map(pooled[0], page_size).ptr if pooled else 0, pooled[1].data_ptr() if pooled else 0,
+          pooled[1].stride(0) if pooled else 0, int(pooled[2]) if pooled else 0, pool_parts, _stream())
     global launches
-    launches += 1          # partition kernel + merge kernel
+    launches += 2 if pooled else 1          # partition kernel(s) + merge kernel
 
 
 def decode_fused_takes(qkv: torch.Tensor, head_dim: int, pool: torch.Tensor, page_size: int, meta,
@@ -1508,16 +1519,16 @@ def sink_attention(q: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Ten
               "sink_attention: the pooled cache has the layout and dtype of the cache, int32 tables and a block size")
         pool_p = int(pooled[2])
     decodes, tiles_left = meta.num_decodes, True
-    fast = (use_sink_attention_mma and pooled is None and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
+    fast = (use_sink_attention_mma and q.dtype == torch.bfloat16 and dim == vdim == HD and HD in (64, 128)
             and meta.error_flag is not None and q.is_contiguous() and q.data_ptr() % 16 == 0)
     extras = dict(keep_first=keep_first, chunk=chunk or 0, softcap=softcap or 0.0, sinks=sinks)
-    if fast and decodes and (not masked or (page_size >= 8 and DECODE_PARTITION % page_size == 0)):
+    if fast and decodes and (not (masked or pooled) or (page_size >= 8 and DECODE_PARTITION % page_size == 0)):
         attention_decode(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window, sink=sink, gate=gate,
-                         **extras)
+                         pooled=pooled, **extras)
         decodes = 0
     if fast and meta.num_tiles > 0 and use_tcgen05_attention and prefill_tcgen05_heads_per_block(num_heads, num_kv_heads, HD, page_size) > 0:
         attention_prefill_tcgen05(q, out, num_heads, num_kv_heads, HD, pool, page_size, block_tables, meta, scale, window,
-                                  sink=sink, gate=gate, **extras)
+                                  sink=sink, gate=gate, pooled=pooled, **extras)
         tiles_left = False
     tiles, n_tiles = meta.tile_lists[SINK_ATTN_TILE_Q]
     if not tiles_left:

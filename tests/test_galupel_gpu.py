@@ -17,10 +17,10 @@ LENGTHS = {"A": (70, 45, 100, 33, 64, 129), "B": (37, 88, 50, 112, 41, 65), "C":
 TOL = {"float32": 3e-5, "bfloat16": 1e-1}
 MEAN_TOL = {"float32": 1e-5, "bfloat16": 3e-2}
 # In bfloat16 a router's close call may go the other way (the random weights here take no care to keep the choice scores
-# apart): that token then runs another expert and is off by tens of per cent, alone.  A model with routers may have a few
-# such positions, in proportion to the router decisions a token meets on its way; in float32, and in a model whose routers
-# take every expert, there is none.
-FLIPS = {"float32": 0.0, "bfloat16": 0.015}
+# apart, and a router decides twice: which groups, then which experts): that token then runs other experts and is off by
+# tens of per cent, alone.  A model with routers may have a few such positions, in proportion to the router decisions a
+# token meets on its way; in float32, and in a model whose routers take every expert, there is none.
+FLIPS = {"float32": 0.0, "bfloat16": 0.04}
 _plain = {}
 
 
@@ -58,16 +58,18 @@ def _routed(cfg):
     return sum(1 for l in cfg["layers"] if l["mlp"] and l["mlp"]["router"]["top"] < l["mlp"]["router"]["experts"])
 
 
-def _check(name, dtype, reqs, got, tag, folder=None, cfg=None):
+def _check(name, dtype, reqs, got, tag, folder=None, cfg=None, tol=None):
+    """``tol``: for models whose scores were sharpened (a float32 score of 40 carries a rounding of 4e-6 into the exponent)."""
     cfg = cfg or zoo.ALL[name][0]
+    tol = tol or TOL[dtype]
     for i, r in enumerate(reqs):
         ref, mine = _plain_logits(name, r, folder), got[f"{tag}{i}"]
         assert mine.shape == ref.shape and np.isfinite(mine).all()
         err = _error(mine, ref)
-        bad = np.nonzero(err > TOL[dtype])[0]
+        bad = np.nonzero(err > tol)[0]
         allowed = max(1, int(np.ceil(FLIPS[dtype] * len(r) * _routed(cfg)))) if _routed(cfg) and FLIPS[dtype] else 0
         assert bad.size <= allowed, (f"model {name} {dtype} cutting {tag!r} request {i}: first wrong token at position {bad[0]} "
-                                     f"(error {err[bad[0]]:.3e}, tolerance {TOL[dtype]}); all: "
+                                     f"(error {err[bad[0]]:.3e}, tolerance {tol}); all: "
                                      + ", ".join(f"{p}: {err[p]:.2e}" for p in bad[:12]) + f"; median {np.median(err):.2e}")
         assert np.median(err) < MEAN_TOL[dtype] and err.mean() < 3 * MEAN_TOL[dtype], f"model {name} {dtype} cutting {tag!r} request {i}: mean error {err.mean():.3e}"
 
@@ -170,7 +172,7 @@ def test_a_far_block_decides_the_logits():
     for steps, tag in ((helpers.trace_whole([r]), "w"), (helpers.trace_decode_tail([r], tail=40), "d"),
                        (helpers.trace_portions([r], sizes=(50, 2, 130, 7)), "p")):
         got, _ = _replay("B", "float32", steps, folder=folder, poison=True)
-        _check("B", "float32", [r], got, tag, folder=folder, cfg=cfg)
+        _check("B", "float32", [r], got, tag, folder=folder, cfg=cfg, tol=2e-4)
 
 
 def test_sharp_scores_at_the_edges_of_windows_and_blocks():
@@ -185,7 +187,7 @@ def test_sharp_scores_at_the_edges_of_windows_and_blocks():
     for steps, tag in ((helpers.trace_whole(reqs), "w"), (helpers.trace_decode_tail(reqs, tail=70), "d"),
                        (helpers.trace_portions(reqs, sizes=(19, 2, 24, 1, 20, 3, 47)), "p")):
         got, _ = _replay("A", "float32", steps, folder=folder, poison=True)
-        _check("A", "float32", reqs, got, tag, folder=folder, cfg=cfg)
+        _check("A", "float32", reqs, got, tag, folder=folder, cfg=cfg, tol=2e-4)
 
 
 def test_blocks_matter():
