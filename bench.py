@@ -28,8 +28,8 @@ GPU: for ``--gpus N`` with N > 1 one line says so and the exit code is 2.
 Modes: ``step`` (the line above), ``offline`` (the reference's own bench.py:38-66 with its options ``--num-seqs
 --budget --chunked --threshold --out --label --expect-gpu``; a JSON row like the reference's is appended to
 ``--out``), ``mixed`` (the 8B workload above, at any shape), ``decode`` (decode at batches ``--batches`` after
-``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen``, ``pugadra`` and ``gevulorn``
-(prefill and decode of that design at the layer sizes ``--sizes``, beside the Qwen3 of equal size (Gevulorn: the Pugadra of equal
+``--prompt-len`` prompts), ``prefill`` (one prompt of ``--prompt-len`` tokens in portions of ``--budget``), ``logozen``, ``pugadra``, ``gevulorn`` and ``galupel``
+(prefill and decode of that design at the layer sizes ``--sizes``, beside the Qwen3 of equal size (Gevulorn and Galupel: the Pugadra of equal
 size), with the time of every kernel).
 """
 from __future__ import annotations
@@ -143,8 +143,38 @@ GEVULORN_SIZES = {   # as PUGADRA_SIZES, then the recurrence's heads / key size 
     "m": _gevulorn(2048, 8, 8192, 16, 4, 128, 1024, 32, 2, 2048, 2048, 8, 128, 256),
     "l": _gevulorn(4096, 6, 12288, 32, 8, 128, 1024, 32, 4, 2048, 4096, 16, 128, 256),
 }
-DESIGN_SIZES = {"logozen": LOGOZEN_SIZES, "pugadra": PUGADRA_SIZES, "gevulorn": GEVULORN_SIZES}
-DESIGN_TWINS = {"logozen": "qwen3", "pugadra": "qwen3", "gevulorn": "pugadra"}      # the model set beside each design
+def _galupel(width, layers, ff, heads, kv_heads, dim, window, pool, experts, top, expert_ff, groups, l_dim, l_rot, l_vdim, l_rank,
+             vocab=32768):
+    """A Galupel of ``layers`` layers: on the even layers attention over a window and pooled blocks (every second of them reads
+    the keys and values of the attention layer before it), on the odd ones attention through a latent with a window; routed
+    experts in groups everywhere; norms in four groups; scaled and capped logits.  And the Pugadra of the same width, depth,
+    heads, head size, window, expert sizes and vocabulary to set beside it."""
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top, "groups": {"count": groups[0], "keep": groups[1]}},
+           "expert": {"ff": expert_ff}}
+
+    def layer(i):
+        if i % 2 == 0:
+            m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window, "pool": pool}}
+            if i % 4 == 2:
+                m["kv_from"] = i - 2
+            return {"type": "attention", "mixer": m, "mlp": moe}
+        m = {"heads": heads, "dim": l_dim, "rot_dim": l_rot, "vdim": l_vdim, "kv_rank": l_rank, "scale": (l_dim + l_rot) ** -0.5,
+             "rot": {"base": 10000.0, "dims": l_rot}, "mask": {"size": window}}
+        return {"type": "latent_attention", "mixer": m, "mlp": moe}
+    cfg = {"architecture": "Galupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5, "groups": 4}, "logit_scale": 0.5,
+           "logit_softcap": 30.0, "layers": [layer(i) for i in range(layers)]}
+    twin, _ = _pugadra(width, layers, ff, heads, kv_heads, dim, window, experts, top, expert_ff, expert_ff, 0, vocab=vocab)
+    return cfg, twin
+
+
+GALUPEL_SIZES = {   # width, layers, the twin's dense ff, heads / kv heads / head size, window, block, experts / chosen / expert ff /
+                    # (groups, kept), the latent layers' unrotated / rotated / value sizes and rank
+    "s": _galupel(1024, 8, 3072, 16, 4, 64, 512, 16, 16, 2, 768, (4, 2), 32, 32, 64, 128),
+    "m": _galupel(2048, 8, 8192, 16, 4, 128, 1024, 32, 32, 2, 2048, (4, 2), 64, 64, 128, 256),
+    "l": _galupel(4096, 6, 12288, 32, 8, 128, 1024, 32, 32, 4, 2048, (8, 4), 64, 64, 128, 512),
+}
+DESIGN_SIZES = {"logozen": LOGOZEN_SIZES, "pugadra": PUGADRA_SIZES, "gevulorn": GEVULORN_SIZES, "galupel": GALUPEL_SIZES}
+DESIGN_TWINS = {"logozen": "qwen3", "pugadra": "qwen3", "gevulorn": "pugadra", "galupel": "pugadra"}      # the model set beside each design
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
@@ -154,8 +184,8 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen", "pugadra", "gevulorn"], default="step")
-    p.add_argument("--sizes", default="s,m", help="logozen, pugadra and gevulorn modes: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
+    p.add_argument("--mode", choices=["step", "offline", "mixed", "decode", "prefill", "logozen", "pugadra", "gevulorn", "galupel"], default="step")
+    p.add_argument("--sizes", default="s,m", help="logozen, pugadra, gevulorn and galupel modes: which of the layer sizes " + ",".join(sorted(LOGOZEN_SIZES)))
     p.add_argument("--shape", choices=sorted(SHAPES), default="0.6b", help="layer sizes, when no --model is given")
     p.add_argument("--extras", type=int, default=1,
                    help="step mode: also run the offline workload, the 8B mixed workload and the 32B decode points")
@@ -832,6 +862,43 @@ def _gevulorn_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> d
     return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_gla_scan", "me_moe_gemm", "me_gemm_tcgen05_grouped"), times, pk)
 
 
+def _galupel_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
+    """What Galupel's own kernels have to move or do in a prefill step of T tokens and the fraction of the measured peak that
+    their summed time makes: bytes for the element-wise kernels, multiply-adds for attention and experts."""
+    W = cfg["width"]
+    need = {k: 0.0 for k in ("me_group_norm", "me_attn_prep", "me_pool_kv", "me_sink_attn", "me_attn_prefill_tcgen05", "me_latent_prep",
+                             "me_latent_attention_mma", "me_moe_gemm", "me_gemm_tcgen05_grouped", "me_activation", "me_moe_combine")}
+    need["me_group_norm"] += T * W * (8 + item) + W * (4 + item)            # behind the embedding, and the last norm's one row
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        subs = 1 + (mlp is not None)
+        need["me_group_norm"] += subs * T * W * (8 + 4 + item)               # stream read and written, y (float32) read, copy written
+        H, V = m["heads"], m["vdim"]
+        size = m.get("mask", {}).get("size")
+        if layer["type"] == "attention":
+            G, D, P = m["kv_heads"], m["dim"], m["mask"].get("pool")
+            own = "kv_from" not in m
+            need["me_attn_prep"] += T * (H + (2 * G if own else 0)) * D * (4 + item)
+            blocks = sum(max(0, p - size + 1) // P for p in range(T)) if P else 0          # (query, block) pairs
+            if P:
+                need["me_pool_kv"] += T * G * (D + V) * item * (1.0 + 1.0 / P)
+            att = 2.0 * H * (D + V) * (_window_pairs(T, size) + blocks)
+            need["me_sink_attn"] += att
+            need["me_attn_prefill_tcgen05"] += att
+        else:
+            C, R = m["kv_rank"], m["rot_dim"]
+            need["me_latent_prep"] += T * ((H * (m["dim"] + R) + C + R) * 4 + (H * (m["dim"] + R) + C + R) * item)
+            need["me_latent_attention_mma"] += 2.0 * H * (2 * C + R) * _window_pairs(T, size)
+        if mlp is not None:
+            pairs, F = T * mlp["router"]["top"], mlp["expert"]["ff"]
+            need["me_moe_gemm"] += 4.0 * pairs * F * W
+            need["me_gemm_tcgen05_grouped"] += 4.0 * pairs * F * W
+            need["me_activation"] += pairs * F * 2 * item
+            need["me_moe_combine"] += T * W * (4 * mlp["router"]["top"] + 4)
+    return _fractions(need, ("me_sink_attn", "me_attn_prefill_tcgen05", "me_latent_attention_mma", "me_moe_gemm", "me_gemm_tcgen05_grouped"),
+                      times, pk)
+
+
 def _qwen3_roofline(cfg: dict, T: int, item: int, pk: dict, times: dict) -> dict:
     """The like kernels of the Qwen3 beside a design: its norm, its q/k preparation and its prompt attention."""
     W, L = cfg["hidden_size"], cfg["num_hidden_layers"]
@@ -855,7 +922,8 @@ def run_design_mode(args, design: str) -> int:
     Pugadra) of the same width, depth, heads, feed-forward width and vocabulary; random weights drawn on the device."""
     import torch
     sizes_of = DESIGN_SIZES[design]
-    rooflines = {"logozen": _logozen_roofline, "pugadra": _pugadra_roofline, "gevulorn": _gevulorn_roofline, "qwen3": _qwen3_roofline}
+    rooflines = {"logozen": _logozen_roofline, "pugadra": _pugadra_roofline, "gevulorn": _gevulorn_roofline, "galupel": _galupel_roofline,
+                 "qwen3": _qwen3_roofline}
     twin_label = DESIGN_TWINS[design]
     pk = peaks()
     item = 2 if args.dtype in ("bfloat16", "bf16") else 4

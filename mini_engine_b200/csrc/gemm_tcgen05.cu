@@ -53,7 +53,10 @@ __device__ __forceinline__ void store_row32(float* dst, const float (&v)[32], in
 
 // The gated epilogue (EPI 1) in its general form: g = min(gate, limit), u = clamp(up, -limit, limit) (limit <= 0: as they
 // are), g * sigmoid(alpha * g) * (u + shift).  SiLU-and-multiply is {0, 1, 0}.
-struct GluParams { float limit = 0.f, alpha = 1.f, shift = 0.f; };
+struct GluParams {
+  float limit = 0.f, alpha = 1.f, shift = 0.f;
+  int act = -1;      // without the gate (EPI 0): an element-wise activation of common.cuh on the results, by number (-1: none)
+};
 __device__ __forceinline__ float gated(float g, float u, const GluParams& p) {
   if (p.limit > 0.f) {
     g = fminf(g, p.limit);
@@ -81,6 +84,10 @@ __device__ __forceinline__ void write_rows(Load&& load, Fix&& fix, unsigned char
       load(c, g);
       tc5::wait_ld();
       fix(c, g);
+      if (glu.act >= 0) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) g[j] = act_apply(g[j], glu.act);
+      }
     }
   };
   if (!vec) {
@@ -941,21 +948,23 @@ ME_API int me_gemm_tcgen05(const void* map_a, const void* map_w, void* C, int c_
 
 // One product per expert over rows in expert order (see gemm_tcgen05_grouped_kernel).  map_a: A [rows, K], boxes 128 x 64;
 // map_w: W as [E * rows_w, K], boxes bn x 64 (glu: bn / 2 x 64, and rows_w = 2 N: gate rows then up rows); bn: 128 or 256.  C [rows, N]:
-// bfloat16 with ``glu`` (the clamped gated activation), float32 or bfloat16 without.  ``rows`` bounds the grid.
+// bfloat16 with ``glu`` 1 (the clamped gated activation), float32 or bfloat16 without; ``glu`` 2 + k: activation k of common.cuh on
+// the plain product.  ``rows`` bounds the grid.
 ME_API int me_gemm_tcgen05_grouped(const void* map_a, const void* map_w, void* C, int c_dtype, int64_t ldc, const int* offsets, int E,
                                    int rows, int N, int rows_w, int K, int glu, float limit, float alpha, float shift, int bn, int* err,
                                    cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   ME_REQUIRE(map_a && map_w && err && offsets, "me_gemm_tcgen05_grouped: missing operand");
-  ME_REQUIRE(K % 8 == 0 && K > 0 && E > 0 && rows_w == (glu ? 2 * N : N), "me_gemm_tcgen05_grouped: K %d, %d experts, %d rows of W for N %d",
+  ME_REQUIRE(K % 8 == 0 && K > 0 && E > 0 && rows_w == (glu == 1 ? 2 * N : N), "me_gemm_tcgen05_grouped: K %d, %d experts, %d rows of W for N %d",
              K, E, rows_w, N);
-  ME_REQUIRE(!glu || c_dtype == ME_BF16, "me_gemm_tcgen05_grouped: the gated activation is written in bfloat16");
+  ME_REQUIRE(glu != 1 || c_dtype == ME_BF16, "me_gemm_tcgen05_grouped: the gated activation is written in bfloat16");
   int rc;
   GluParams gp;
   gp.limit = limit, gp.alpha = alpha, gp.shift = shift;
+  gp.act = glu >= 2 ? glu - 2 : -1;
   ME_REQUIRE(bn == 128 || bn == 256, "me_gemm_tcgen05_grouped: tile width %d is not 128 or 256", bn);
 #define ME_GROUPED(BN_)                                                                                                          \
-  if (glu) rc = launch_grouped<BN_, 1, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);             \
+  if (glu == 1) rc = launch_grouped<BN_, 1, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream);        \
   else if (c_dtype == ME_F32) rc = launch_grouped<BN_, 0, float>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream); \
   else rc = launch_grouped<BN_, 0, bf16>(map_a, map_w, C, ldc, offsets, E, rows, N, rows_w, K, gp, err, stream)
   if (bn == 256) { ME_GROUPED(256); } else { ME_GROUPED(128); }

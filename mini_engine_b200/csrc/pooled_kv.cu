@@ -9,6 +9,8 @@
 // One block of threads = one token x one kv head.
 #include "common.cuh"
 
+constexpr int PK_PER_THREAD = 4;      // elements of a key and a value together that a thread sums: D + Dv <= 512
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 pool_kv_kernel(const T* __restrict__ pool, const int* __restrict__ block_tables, int bt_stride, T* __restrict__ pooled,
@@ -27,17 +29,41 @@ pool_kv_kernel(const T* __restrict__ pool, const int* __restrict__ block_tables,
   const int64_t plane = (int64_t)nkv * page_size * HD;
   T* dst = pooled + (((int64_t)dst_page * 2 * nkv + kvh) * page_size + (b % page_size)) * HD;
   const float inv = 1.0f / (float)P;
-  for (int d = threadIdx.x; d < D + Dv; d += blockDim.x) {
-    const bool is_k = d < D;
-    float sum = 0.f;
-    for (int j = p + 1 - P; j <= p; ++j) {
+  // The block's rows are found once (128 positions at a time), then every thread sums its elements over them with eight
+  // loads in flight; the sums run in the order of the positions.
+  __shared__ int64_t row_at[128];
+  float acc[PK_PER_THREAD];
+#pragma unroll
+  for (int e = 0; e < PK_PER_THREAD; ++e) acc[e] = 0.f;
+  for (int j0 = p + 1 - P; j0 <= p; j0 += 128) {
+    const int n = min(128, p + 1 - j0);
+    __syncthreads();
+    if (threadIdx.x < n) {
+      const int j = j0 + threadIdx.x;
       const int page = bt[j / page_size];
-      if (page < 0) continue;
-      const int64_t at = (((int64_t)page * 2 * nkv + kvh) * page_size + (j % page_size)) * HD;
-      sum += to_f<T>(is_k ? pool[at + d] : pool[at + plane + d - D]);
+      row_at[threadIdx.x] = page < 0 ? -1 : (((int64_t)page * 2 * nkv + kvh) * page_size + (j % page_size)) * HD;
     }
-    if (is_k) dst[d] = from_f<T>(sum * inv);
-    else dst[plane + d - D] = from_f<T>(sum * inv);
+    __syncthreads();
+#pragma unroll
+    for (int e = 0; e < PK_PER_THREAD; ++e) {
+      const int d = threadIdx.x + e * 128;
+      if (d >= D + Dv) break;
+      const int64_t off = d < D ? d : plane + d - D;
+      float sum = acc[e];
+#pragma unroll 8
+      for (int jj = 0; jj < n; ++jj) {
+        const int64_t at = row_at[jj];
+        sum += at < 0 ? 0.f : to_f<T>(pool[at + off]);
+      }
+      acc[e] = sum;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < PK_PER_THREAD; ++e) {
+    const int d = threadIdx.x + e * 128;
+    if (d >= D + Dv) break;
+    if (d < D) dst[d] = from_f<T>(acc[e] * inv);
+    else dst[plane + d - D] = from_f<T>(acc[e] * inv);
   }
 }
 
@@ -47,7 +73,7 @@ ME_API int me_pool_kv(const void* pool, const int* block_tables, int bt_stride, 
                       int pbt_stride, const int* positions, const int* token_req, int dtype, int T, int P, int nkv, int D, int Dv,
                       int HD, int page_size, cudaStream_t stream) {
   if (T == 0) return 0;
-  ME_REQUIRE(T > 0 && P >= 1 && nkv >= 1 && nkv <= 65535 && D >= 1 && Dv >= 1 && HD >= D && HD >= Dv && page_size >= 1,
+  ME_REQUIRE(T > 0 && P >= 1 && nkv >= 1 && nkv <= 65535 && D >= 1 && Dv >= 1 && D + Dv <= 128 * PK_PER_THREAD && HD >= D && HD >= Dv && page_size >= 1,
              "me_pool_kv: bad sizes P=%d kv heads=%d D=%d Dv=%d HD=%d", P, nkv, D, Dv, HD);
   ME_DISPATCH_DTYPE(dtype, TT, me_launch(pool_kv_kernel<TT>, dim3(T, nkv), dim3(128), 0, stream, (const TT*)pool, block_tables, bt_stride,
                                          (TT*)pooled, pooled_tables, pbt_stride, positions, token_req, P, nkv, D, Dv, HD, page_size));

@@ -66,6 +66,7 @@ _PROTOS = {
     "me_add_row_vector": [_P, _I, _I, _I, _P, _P],
     "me_moe_route": [_P, _P, _I, _I, _I, _P, _P, _P],
     "me_moe_route_grouped": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
+    "me_moe_route_grouped_sort": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_group_norm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
     "me_pool_kv": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
@@ -1377,11 +1378,6 @@ def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
     _call("me_activation", x.data_ptr(), _dt(x), x.stride(0), out.data_ptr(), _dt(out), out.stride(0), T, F, ACTIVATIONS[kind], _stream())
 
 
-def _activation_in_place(x: torch.Tensor, kind: str) -> None:
-    _call("me_activation", x.data_ptr(), _dt(x), x.stride(0), x.data_ptr(), _dt(x), x.stride(0), x.shape[0], x.shape[1], ACTIVATIONS[kind],
-          _stream())
-
-
 def soft_cap(x: torch.Tensor, cap: Optional[float], scale: float = 1.0) -> None:
     """``x <- cap * tanh(scale * x / cap)`` in place (float32); without a cap ``x <- scale * x``."""
     _need(x.dtype == torch.float32 and x.is_contiguous() and (cap is None or cap > 0), "soft_cap: float32 values and a positive cap")
@@ -1566,6 +1562,20 @@ def moe_route_grouped(logits: torch.Tensor, correction: Optional[torch.Tensor], 
           _stream())
 
 
+def moe_route_grouped_sort(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, idx: torch.Tensor,
+                           weights: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor, place: torch.Tensor) -> None:
+    """``moe_route_grouped`` and ``moe_sort`` together; a step of few tokens does both in one kernel."""
+    T, E = logits.shape
+    _need(logits.dtype == torch.float32 and logits.is_contiguous() and (correction is None or (correction.dtype == torch.float32 and correction.numel() == E)),
+          "moe_route_grouped_sort: logits and correction must be float32")
+    _need(idx.dtype == torch.int32 and weights.dtype == torch.float32 and tuple(idx.shape) == tuple(weights.shape) == (T, top)
+          and idx.is_contiguous() and weights.is_contiguous(), "moe_route_grouped_sort: outputs are [T, top]")
+    _need(all(t.dtype == torch.int32 and t.is_contiguous() for t in (counts, offsets, order, place)) and counts.numel() >= E
+          and offsets.numel() >= E + 1 and order.numel() >= T * top and place.numel() >= T * top, "moe_route_grouped_sort: output sizes")
+    _call("me_moe_route_grouped_sort", logits.data_ptr(), _ptr(correction), T, E, top, int(groups), int(keep), idx.data_ptr(),
+          weights.data_ptr(), counts.data_ptr(), offsets.data_ptr(), order.data_ptr(), place.data_ptr(), _stream())
+
+
 def moe_sort(idx: torch.Tensor, num_experts: int, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor,
              place: torch.Tensor) -> None:
     """Group the (token, choice) pairs of ``idx`` [T, top] by expert: ``offsets`` [E + 1], ``order`` (pair ids in expert order,
@@ -1604,7 +1614,7 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
     without it, lie in expert order already; ``out`` [pairs, N] in expert order.  ``glu`` = (limit, alpha[, shift]): the weight holds gate
     rows then up rows and the result is the gated activation g sigmoid(alpha g) (u + shift), clamped by a positive limit (shift 1
     when it is not given).  ``activation`` (a key of ``ACTIVATIONS``, instead of ``glu``): that function of the plain product, in the
-    product's epilogue on the CUDA cores and in the mma.sync kernel, as a pass of its own behind the tcgen05 kernel.
+    product's epilogue in all three kernels.
 
     bfloat16 operands with K a multiple of 8 run on the tensor cores: from ``MOE_TCGEN05_MIN_ROWS`` pairs on (and with
     ``workspace`` and ``err`` given) the tcgen05 kernel of csrc/gemm_tcgen05.cu over rows brought into expert order first,
@@ -1627,10 +1637,8 @@ def moe_gemm(a: torch.Tensor, order: Optional[torch.Tensor], top: int, weight: t
         if a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0:
             bn = moe_tcgen05_tile_n if moe_tcgen05_tile_n else (256 if N >= 256 else 128)
             _call("me_gemm_tcgen05_grouped", matrix_tensor_map(a, 128).ptr, matrix_tensor_map(weight.view(E * NN, K), bn // 2 if glu else bn).ptr,
-                  out.data_ptr(), _dt(out), out.stride(0), offsets.data_ptr(), E, rows, N, NN, K, 1 if glu else 0, float(limit),
+                  out.data_ptr(), _dt(out), out.stride(0), offsets.data_ptr(), E, rows, N, NN, K, epi, float(limit),
                   float(alpha), float(shift), bn, err.data_ptr(), _stream())
-            if activation:
-                _activation_in_place(out, activation)
             return
         order = None
     _call("me_moe_gemm", a.data_ptr(), _dt(a), a.stride(0), _ptr(order), top, weight.data_ptr(), _dt(weight), weight.stride(0),

@@ -136,8 +136,8 @@ class RoutedExperts(FeedForward):
         order = ctx.buffer("moe_order", (T * top,), torch.int32)
         place = ctx.buffer("moe_place", (T * top,), torch.int32)
         if self.routing == "sigmoid_groups":
-            ops.moe_route_grouped(z, self.p("correction") if self.has_correction else None, top, *self.groups, idx, wgt)
-            ops.moe_sort(idx, E, counts, offsets, order, place)
+            ops.moe_route_grouped_sort(z, self.p("correction") if self.has_correction else None, top, *self.groups, idx, wgt, counts,
+                                       offsets, order, place)
         else:
             ops.moe_route_sort(z, self.p("router.b") if self.has_router_bias else None, top, idx, wgt, counts, offsets, order, place)
         act = ctx.buffer("moe_act", (T * top, F), ctx.act_dtype)

@@ -89,9 +89,29 @@ def test_grouped_routing_against_the_plain_rule(E, top, count, keep):
         assert (mine_w - ref_full)[clear].abs().max() < 1e-6                               # the plain sigmoid, correction left out
 
 
-def test_expert_products_with_the_exact_gelu():
+def test_routing_and_grouping_of_a_small_step_in_one_kernel():
     ops = _ops()
-    T, W, F, E, top = 40, 48, 24, 4, 2
+    for T, E, top, count, keep in ((20, 12, 3, 3, 2), (1, 8, 4, 2, 1), (64, 16, 2, 4, 2)):
+        z = torch.randn(T, E, generator=g(T)) * 2.0
+        corr = torch.randn(E, generator=g(T + 1)) * 0.5
+        mk = lambda *shape, dt=torch.int32: torch.empty(*shape, dtype=dt, device=DEV)
+        idx0, w0 = mk(T, top), mk(T, top, dt=torch.float32)
+        ops.moe_route_grouped(z.to(DEV), corr.to(DEV), top, count, keep, idx0, w0)
+        idx, w, counts, offsets, order, place = mk(T, top), mk(T, top, dt=torch.float32), mk(E), mk(E + 1), mk(T * top), mk(T * top)
+        ops.moe_route_grouped_sort(z.to(DEV), corr.to(DEV), top, count, keep, idx, w, counts, offsets, order, place)
+        assert torch.equal(idx, idx0) and torch.equal(w, w0)
+        flat, off = idx.cpu().reshape(-1), offsets.cpu()
+        assert off[0] == 0 and off[-1] == T * top
+        for e in range(E):
+            pairs = order.cpu()[off[e]:off[e + 1]]
+            assert torch.equal(pairs, torch.nonzero(flat == e).reshape(-1).to(torch.int32))        # token order inside an expert
+        assert torch.equal(order.cpu()[place.cpu().long()], torch.arange(T * top, dtype=torch.int32))
+
+
+@pytest.mark.parametrize("T, W, F", [(40, 48, 24), (400, 64, 96)])       # (800 pairs: bfloat16 takes the tcgen05 product)
+def test_expert_products_with_the_exact_gelu(T, W, F):
+    ops = _ops()
+    E, top = 4, 2
     x = torch.randn(T, W, generator=g(1))
     w = torch.randn(E, F, W, generator=g(2)) * 0.3
     idx = torch.stack([torch.randperm(E, generator=g(10 + t))[:top] for t in range(T)]).to(torch.int32)
@@ -103,9 +123,12 @@ def test_expert_products_with_the_exact_gelu():
         place = torch.empty(T * top, dtype=torch.int32, device=DEV)
         ops.moe_sort(idx.to(DEV), E, counts, offsets, order, place)
         out = torch.empty(T * top, F, dtype=dt, device=DEV)
-        ops.moe_gemm(x.to(DEV).to(dt), order, top, w.to(DEV).to(dt), offsets, out, activation="gelu")
+        err = torch.zeros(4, dtype=torch.int32, device=DEV)
+        ops.moe_gemm(x.to(DEV).to(dt), order, top, w.to(DEV).to(dt), offsets, out, activation="gelu", err=err,
+                     workspace=lambda name, shape, dtype: torch.empty(shape, dtype=dtype, device=DEV))
+        assert int(err.abs().sum()) == 0
         xr, wr = x.to(dt).double(), w.to(dt).double()
-        for t in range(T):
+        for t in range(0, T, max(1, T // 40)):
             for k in range(top):
                 ref = torch.nn.functional.gelu(xr[t] @ wr[idx[t, k]].T)
                 got = out[place[t * top + k]].cpu().double()
