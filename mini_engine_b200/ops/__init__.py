@@ -68,7 +68,7 @@ _PROTOS = {
     "me_moe_route_grouped": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P],
     "me_moe_route_grouped_sort": [_P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_group_norm": [_P, _P, _I, _L, _P, _I, _F, _P, _I, _P, _I, _I, _P],
-    "me_pool_kv": [_P, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "me_pool_kv": [_P, _P, _I, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "me_moe_sort": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
     "me_moe_route_sort": [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P],
     "me_moe_gemm": [_P, _I, _L, _P, _I, _P, _I, _L, _P, _I, _P, _I, _L, _I, _I, _I, _I, _F, _F, _F, _I, _P],
@@ -1302,20 +1302,27 @@ def group_norm(residual: torch.Tensor, y: Optional[torch.Tensor], weight: torch.
           weight.data_ptr(), int(groups), float(eps), _ptr(out), _dt(out) if out is not None else 0, _ptr(rows), n, W, _stream())
 
 
+POOL_BY_BLOCK_MAX_REQUESTS = 64    # steps with prompts of up to this many requests: a block of threads per completed block of tokens
+
+
 def pool_kv(pool: torch.Tensor, block_tables: torch.Tensor, pooled: torch.Tensor, pooled_tables: torch.Tensor, positions: torch.Tensor,
-            token_req: torch.Tensor, block: int, dim: int, vdim: int, page_size: int) -> None:
+            token_req: torch.Tensor, block: int, dim: int, vdim: int, page_size: int, meta=None) -> None:
     """Behind a step's cache write: for every token of the step whose position ends a block of ``block`` tokens, the mean of the
     block's keys and the mean of its values (as ``pool`` holds them) go to row position // block of ``pooled``, a cache of the
-    same layout with block tables of its own (see csrc/pooled_kv.cu)."""
+    same layout with block tables of its own (see csrc/pooled_kv.cu).  ``meta`` (the step's shape): a step that brings portions
+    of prompts for a few requests launches a block of threads for every block of tokens it can complete instead of one a token."""
     T = positions.numel()
+    by_block = (meta is not None and meta.num_decodes < meta.num_reqs and meta.num_reqs <= POOL_BY_BLOCK_MAX_REQUESTS
+                and meta.num_tokens == T)
     _need(pool.dim() == 5 and pool.shape[1] == 2 and pool.is_contiguous() and pooled.is_contiguous() and pooled.dtype == pool.dtype
           and pooled.shape[1:] == pool.shape[1:], "pool_kv: both caches are [pages, 2, kv heads, page, row] of one dtype")
     _need(block_tables.dtype == pooled_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and pooled_tables.stride(1) == 1,
           "pool_kv: block tables")
     _need(token_req.numel() == T and block >= 1, "pool_kv: a request for every token and a block size")
     _call("me_pool_kv", pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), pooled.data_ptr(), pooled_tables.data_ptr(),
-          pooled_tables.stride(0), positions.data_ptr(), token_req.data_ptr(), _dt(pool), T, int(block), pool.shape[2], dim, vdim,
-          pool.shape[-1], page_size, _stream())
+          pooled_tables.stride(0), positions.data_ptr(), token_req.data_ptr(), meta.cu_seqlens.data_ptr() if by_block else 0,
+          meta.context_lens.data_ptr() if by_block else 0, meta.num_reqs if by_block else 0, 1 if by_block else 0, _dt(pool), T, int(block),
+          pool.shape[2], dim, vdim, pool.shape[-1], page_size, _stream())
 
 
 # ---- norms on both sides of a sub-layer, convolved and gated attention with a sink, routed feed-forwards ----------------

@@ -92,7 +92,7 @@ class PooledWindowAttention(Mixer):
             pv = ctx.kv_cache(call.cache_slot, "pooled")
             if call.writes_cache:
                 ops.pool_kv(kv.pool, kv.block_tables, pv.pool, pv.block_tables, ctx.positions, ctx.token_req, self.pool, D, V,
-                            kv.page_size)
+                            kv.page_size, meta=ctx.attn_meta)
             pooled = (pv.pool, pv.block_tables, self.pool)
         out = ctx.buffer("attn_out", (T, H * V), ctx.act_dtype)
         ops.sink_attention(q, None, out, kv.pool, kv.page_size, kv.block_tables, ctx.attn_meta, H, G, D, V, self.scale,

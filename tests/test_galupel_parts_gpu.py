@@ -177,7 +177,10 @@ class _Caches:
         for b, n in enumerate(lengths):
             pos = torch.arange(n, dtype=torch.int32)
             for lo, hi in ((0, n // 3), (n // 3, n // 3 + 1), (n // 3 + 1, n)):
-                if hi > lo:
+                if hi - lo > 1 and lo > 0:          # as a step of one request's portion: a launch by completed blocks
+                    ops.pool_kv(self.pool, self.bt[b:b + 1], self.pooled, self.pbt[b:b + 1], pos[lo:hi].to(DEV).contiguous(),
+                                torch.zeros(hi - lo, dtype=torch.int32, device=DEV), P, D, Dv, page, meta=_meta([hi - lo], [hi]))
+                elif hi > lo:                       # a launch by tokens
                     ops.pool_kv(self.pool, self.bt, self.pooled, self.pbt, pos[lo:hi].to(DEV).contiguous(),
                                 torch.full((hi - lo,), b, dtype=torch.int32, device=DEV), P, D, Dv, page)
 
