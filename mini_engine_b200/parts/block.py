@@ -293,6 +293,16 @@ class PostNormBlock(Block):
             if norm is not None and not hasattr(norm, "add_normed"):
                 raise ValueError("a 'post_norm' block needs norms that can add a normalised output to the stream (kind 'group_rmsnorm')")
 
+    def param_decls(self):
+        """A layer without a feed-forward has no use for the second norm; files that hold one all the same are accepted."""
+        if self.feed_forward is not None:
+            return []
+        spec = self.spec.feed_forward_norm or self.spec.norm
+        if spec is None or "size" not in spec.args:
+            return []
+        return [ParamDecl(self.spec.feed_forward_norm_prefix + spec.args.get("param", "weight"), (spec.args["size"],), role="vector",
+                          optional=True)]
+
     def forward(self, residual, delta, ctx, call, upcoming=None):
         if isinstance(delta, StreamCopy):
             x = delta.x

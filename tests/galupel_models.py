@@ -78,7 +78,19 @@ C = config(130, 128, [
     attn(8, 2, 64, 64, size=48, pool=32, kv_from=0, mlp=moe(8, 2, 32)),
 ], eps=1e-5, groups=4, scale=0.5, cap=20.0)
 
-ALL = {"A": (A, 1, 16), "B": (B, 2, 8), "C": (C, 3, 16)}        # config, seed, page size
+# D: a latent layer first; two lenders and a borrower behind each; heads of 128 on one kv head and heads of 32 with values of 64;
+#    windows of several pages; every expert in one group and one chosen; a latent of 64 + 32 (the tensor-core sizes) and one of
+#    40 + 24 with half of it rotated; pages of 32
+D = config(300, 256, [
+    latent(4, 32, 32, 48, 64, size=70, rot=32, base=20000.0, mlp=moe(4, 1, 64)),
+    attn(4, 1, 128, 128, size=90, pool=10, mlp=moe(6, 3, 32, groups=(2, 1))),
+    attn(6, 2, 32, 64, size=40, pool=24, mlp=None),
+    attn(8, 1, 128, 128, size=33, pool=32, kv_from=1, mlp=moe(4, 2, 48, groups=(4, 2))),
+    latent(5, 24, 24, 16, 40, size=50, rot=12, base=300.0, mlp=moe(8, 2, 40, groups=(2, 2))),
+    attn(2, 2, 32, 64, size=100, pool=7, kv_from=2, mlp=moe(5, 5, 24)),
+], eps=1e-5, groups=2, scale=0.3, cap=15.0)
+
+ALL = {"A": (A, 1, 16), "B": (B, 2, 8), "C": (C, 3, 16), "D": (D, 4, 32)}        # config, seed, page size
 
 
 def tensors(cfg: dict, seed: int, gain: float = 1.2) -> dict[str, torch.Tensor]:

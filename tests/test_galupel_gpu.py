@@ -10,7 +10,8 @@ import helpers
 import plain_galupel
 
 pytestmark = pytest.mark.gpu
-LENGTHS = {"A": (70, 45, 100, 33, 64, 129), "B": (37, 88, 50, 112, 41, 65), "C": (150, 33, 97, 64, 200, 41)}
+LENGTHS = {"A": (70, 45, 100, 33, 64, 129), "B": (37, 88, 50, 112, 41, 65), "C": (150, 33, 97, 64, 200, 41),
+           "D": (210, 47, 130, 64, 300, 95)}
 # Centred difference of a position's logits, root mean square over the vocabulary, relative to that of the logits: the
 # worst position, and the mean over a request's positions.  bfloat16 rounds activations to 8 bits between the parts,
 # which costs these narrow models a few per cent at some positions; a wrong key, block, window or expert costs tens.
@@ -75,7 +76,7 @@ def _check(name, dtype, reqs, got, tag, folder=None, cfg=None, tol=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_whole(reqs), poison=True)
@@ -83,7 +84,7 @@ def test_each_request_alone_and_whole(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_prompt_then_token_by_token(name, dtype):
     """The tails are longer than every window and block but C's widest, so their edges pass over decoded tokens."""
     reqs = _requests(name)
@@ -92,7 +93,7 @@ def test_prompt_then_token_by_token(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(name, dtype):
     reqs = _requests(name)
     got, _ = _replay(name, dtype, helpers.trace_portions(reqs), poison=True)
@@ -102,7 +103,7 @@ def test_portions_of_changing_size(name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_batches_with_pages_used_again(name, dtype):
     reqs = _requests(name) + _requests(name)[:4]
     steps = helpers.trace_mixed(reqs, max_live=4, seed=3)
